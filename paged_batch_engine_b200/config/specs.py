@@ -44,11 +44,14 @@ class RunStep:
     ``block``: index into ``ModelSpec.blocks`` (a block may be named twice).
     ``cache_layer``: which cache layer this execution uses; two run steps that name
     the same cache layer share it.  ``writes_cache``: False lets a layer read the
-    keys and values another layer wrote without writing its own.
+    keys and values another layer wrote without writing its own.  ``input_mix``: the name of a
+    [W, 2W] tensor M; right before this run step the residual x becomes M [x ; e], e being the
+    embedding output of the step's rows (a pass over a run of layers that re-reads the input).
     """
     block: int
     cache_layer: int
     writes_cache: bool = True
+    input_mix: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -67,6 +70,8 @@ class ModelSpec:
     residual_streams: int = 1      # parallel residual streams (all start as the embedding, summed at the end)
     logit_scale: float = 1.0       # the head's output is multiplied by it
     logit_softcap: Optional[float] = None   # c: logits <- c * tanh(logits / c), after the scale
+    embedding_scale: float = 1.0   # the token's embedding row is multiplied by it
+    position_table_name: Optional[str] = None   # a learned [max_position, W] table whose row p is added (unscaled)
 
     @property
     def num_cache_layers(self) -> int:

@@ -169,11 +169,13 @@ PBE_EXPORT int pbe_add_rmsnorm(float* residual, const void* delta, int delta_dty
 // A layer whose mixer and feed-forward read the same residual: x += (a + b) where a and b are the
 // two branches of the layer before (either may be absent), then y1 = g1 * x * r and y2 = g2 * x * r
 // with the one r = rsqrt(mean(x^2) + eps) both norms share.  g2 == nullptr: one output only.
+// delta_scale m: x += m * (a + b) (a design that scales its branches before the residual sum).
 template <typename TD, typename TO>
 __global__ void add2_rmsnorm2_kernel(float* __restrict__ residual, const TD* __restrict__ delta_a,
                                      const TD* __restrict__ delta_b, const float* __restrict__ gain1,
                                      const float* __restrict__ gain2, TO* __restrict__ out1, TO* __restrict__ out2,
-                                     const int32_t* __restrict__ row_index, int d, float eps) {
+                                     const int32_t* __restrict__ row_index, int d, float eps,
+                                     float delta_scale) {
   __shared__ float red[33];
   extern __shared__ __align__(16) float row[];
   pdl_launch_dependents();
@@ -189,7 +191,7 @@ __global__ void add2_rmsnorm2_kernel(float* __restrict__ residual, const TD* __r
     float add = 0.f;
     if (da) add = to_float(da[i]);
     if (db) add += to_float(db[i]);
-    const float v = res[i] + add;
+    const float v = delta_scale == 1.0f ? res[i] + add : fmaf(delta_scale, add, res[i]);
     row[i] = v;
     ss += v * v;
   }
@@ -204,7 +206,8 @@ __global__ void add2_rmsnorm2_kernel(float* __restrict__ residual, const TD* __r
 
 PBE_EXPORT int pbe_add2_rmsnorm2(float* residual, const void* delta_a, const void* delta_b, int delta_dtype,
                                  const float* gain1, const float* gain2, void* out1, void* out2, int out_dtype,
-                                 const int32_t* row_index, int num_rows, int d, float eps, cudaStream_t stream) {
+                                 const int32_t* row_index, int num_rows, int d, float eps, float delta_scale,
+                                 cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
   const size_t smem = (size_t)d * sizeof(float);
@@ -218,7 +221,8 @@ PBE_EXPORT int pbe_add2_rmsnorm2(float* residual, const void* delta_a, const voi
       opted = 200 * 1024;                                                                          \
     }                                                                                              \
     launch_k(add2_rmsnorm2_kernel<TD, TO>, num_rows, threads, smem, stream, residual,              \
-             (const TD*)delta_a, (const TD*)delta_b, gain1, gain2, (TO*)out1, (TO*)out2, row_index, d, eps); \
+             (const TD*)delta_a, (const TD*)delta_b, gain1, gain2, (TO*)out1, (TO*)out2, row_index, d, eps, \
+             delta_scale);                                                                         \
   } while (0)
   if (delta_dtype == PBE_F32 && out_dtype == PBE_F32) LAUNCH2(float, float);
   else if (delta_dtype == PBE_BF16 && out_dtype == PBE_BF16) LAUNCH2(__nv_bfloat16, __nv_bfloat16);
@@ -368,6 +372,117 @@ PBE_EXPORT int pbe_silu_mul(const void* in, void* out, int dtype, int rows, int 
   else
     launch_k(silu_mul_kernel<__nv_bfloat16>, (int)blocks, threads, 0, stream, (const __nv_bfloat16*)in,
              (__nv_bfloat16*)out, inter, total);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- scaled embedding + learned position row
+// out[t] = table[ids[t]] * scale + pos_table[positions[t]] (the position row unscaled), float32.
+template <typename TW>
+__global__ void embedding_pos_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                                     const int32_t* __restrict__ ids, float scale, const TW* __restrict__ pos_table,
+                                     const int32_t* __restrict__ positions, int max_pos, int d, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * d;
+  const bool ok = id >= 0 && id < vocab;       // the host rejects such ids before launch
+  const TW* row = table + (size_t)(ok ? id : 0) * d;
+  const int pos = pos_table ? positions[t] : -1;
+  const TW* prow = (pos >= 0 && pos < max_pos) ? pos_table + (size_t)pos * d : nullptr;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = ok ? to_float(row[i]) * scale : 0.f;
+    if (prow) v += to_float(prow[i]);
+    o[i] = v;
+  }
+}
+
+PBE_EXPORT int pbe_embedding_pos(float* out, const void* table, int table_dtype, const int32_t* ids, float scale,
+                                 const void* pos_table, const int32_t* positions, int max_pos, int num_tokens,
+                                 int d, int vocab, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int threads = d >= 1024 ? 256 : 128;
+  if (table_dtype == PBE_F32)
+    launch_k(embedding_pos_kernel<float>, num_tokens, threads, 0, stream, out, (const float*)table, ids, scale,
+             (const float*)pos_table, positions, max_pos, d, vocab);
+  else
+    launch_k(embedding_pos_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, out, (const __nv_bfloat16*)table,
+             ids, scale, (const __nv_bfloat16*)pos_table, positions, max_pos, d, vocab);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- [x + m (a + b) ; x0] as a product's operand
+// out[t] = [residual[t] + delta_scale * (a[t] + b[t]) | first[t]], both halves d wide, in the run
+// dtype: the operand of a projection that reads the current residual beside the embedding output.
+template <typename TD, typename TO>
+__global__ void fold_pair_kernel(const float* __restrict__ residual, const TD* __restrict__ delta_a,
+                                 const TD* __restrict__ delta_b, float delta_scale, const float* __restrict__ first,
+                                 TO* __restrict__ out, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float add = 0.f;
+    if (delta_a) add = to_float(delta_a[t * d + i]);
+    if (delta_b) add += to_float(delta_b[t * d + i]);
+    out[t * 2 * d + i] = from_float<TO>(fmaf(delta_scale, add, residual[t * d + i]));
+    out[t * 2 * d + d + i] = from_float<TO>(first[t * d + i]);
+  }
+}
+
+PBE_EXPORT int pbe_fold_pair(const float* residual, const void* delta_a, const void* delta_b, int delta_dtype,
+                             float delta_scale, const float* first, void* out, int out_dtype, int rows, int d,
+                             cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int threads = d >= 1024 ? 256 : 128;
+#define FOLD(TD, TO) launch_k(fold_pair_kernel<TD, TO>, rows, threads, 0, stream, residual, (const TD*)delta_a, \
+                              (const TD*)delta_b, delta_scale, first, (TO*)out, d)
+  if (delta_dtype == PBE_F32 && out_dtype == PBE_F32) FOLD(float, float);
+  else if (delta_dtype == PBE_BF16 && out_dtype == PBE_BF16) FOLD(__nv_bfloat16, __nv_bfloat16);
+  else if (delta_dtype == PBE_F32 && out_dtype == PBE_BF16) FOLD(float, __nv_bfloat16);
+  else FOLD(__nv_bfloat16, float);
+#undef FOLD
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- gated activations other than silu(g) * u
+// in: [rows, 2*inter], gate in columns [0, inter), linear part in [inter, 2*inter); out [rows, inter].
+// kind 1 (capped swish): g <- min(g, limit), u <- clamp(u, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1).
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, size_t total, int kind,
+                               float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = idx / inter;
+    const int c = (int)(idx - r * inter);
+    float g = to_float(in[r * 2 * inter + c]);
+    float u = to_float(in[r * 2 * inter + inter + c]);
+    float y;
+    if (kind == 1) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      y = (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+    } else {
+      y = (g / (1.0f + expf(-g))) * u;
+    }
+    out[idx] = from_float<T>(y);
+  }
+}
+
+PBE_EXPORT int pbe_glu_act(const void* in, void* out, int dtype, int rows, int inter, int kind, float limit,
+                           float alpha, cudaStream_t stream) {
+  const size_t total = (size_t)rows * inter;
+  if (total == 0) return 0;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == PBE_F32)
+    launch_k(glu_act_kernel<float>, (int)blocks, 256, 0, stream, (const float*)in, (float*)out, inter, total, kind,
+             limit, alpha);
+  else
+    launch_k(glu_act_kernel<__nv_bfloat16>, (int)blocks, 256, 0, stream, (const __nv_bfloat16*)in,
+             (__nv_bfloat16*)out, inter, total, kind, limit, alpha);
   return launch_status();
 }
 

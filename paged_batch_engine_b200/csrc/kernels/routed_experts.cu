@@ -136,6 +136,8 @@ struct ExpertRowsParams {
   float* hidden;             // [T * top, F] scratch: silu(gate) * up of every pair
   float* part;               // [T, top, W]
   int T, W, F, top;
+  int act;                   // 0: silu(g) * u; 1: g <- min(g, limit), u <- clamp(u, +-limit), g sigmoid(alpha g) (u + 1)
+  float limit, alpha;
 };
 
 // dot product of a weight row with a float32 vector in shared memory, the lanes along the row;
@@ -194,7 +196,16 @@ __global__ void __launch_bounds__(ER_WARPS * 32) expert_hidden_kernel(ExpertRows
   for (int f = blockIdx.y * ER_UNITS + warp; f < f_end; f += ER_WARPS) {
     const float g = dot_row(wg + (size_t)f * p.W, xs, p.W, lane);
     const float u = dot_row(wu + (size_t)f * p.W, xs, p.W, lane);
-    if (lane == 0) p.hidden[(size_t)pair * p.F + f] = (g / (1.0f + expf(-g))) * u;
+    if (lane == 0) {
+      float h;
+      if (p.act == 1) {
+        const float gc = fminf(g, p.limit), uc = fminf(fmaxf(u, -p.limit), p.limit);
+        h = (gc / (1.0f + expf(-p.alpha * gc))) * (uc + 1.0f);
+      } else {
+        h = (g / (1.0f + expf(-g))) * u;
+      }
+      p.hidden[(size_t)pair * p.F + f] = h;
+    }
   }
 }
 
@@ -306,9 +317,10 @@ PBE_EXPORT int pbe_route(const float* logits, int32_t* chosen, float* weights, i
 
 PBE_EXPORT int pbe_expert_rows(const void* x, const void* w_gate, const void* w_up, long long gu_stride,
                                const void* w_down, const int32_t* chosen, const float* weights, float* hidden,
-                               float* part, void* out, int dtype, int T, int W, int F, int top, cudaStream_t stream) {
+                               float* part, void* out, int dtype, int T, int W, int F, int top, int act, float limit,
+                               float alpha, cudaStream_t stream) {
   if (T <= 0) return 0;
-  ExpertRowsParams p{x, w_gate, w_up, gu_stride, w_down, chosen, weights, hidden, part, T, W, F, top};
+  ExpertRowsParams p{x, w_gate, w_up, gu_stride, w_down, chosen, weights, hidden, part, T, W, F, top, act, limit, alpha};
   const size_t smem1 = sizeof(float) * (size_t)W, smem2 = sizeof(float) * (size_t)F;
   if (smem1 > 200 * 1024 || smem2 > 200 * 1024) return (int)cudaErrorInvalidValue;
   dim3 grid1(T * top, (F + ER_UNITS - 1) / ER_UNITS), grid2(T * top, (W + ER_UNITS - 1) / ER_UNITS);

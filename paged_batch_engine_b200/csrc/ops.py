@@ -108,6 +108,69 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> torc
     return out
 
 
+def embedding_positions(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float,
+                        pos_table: Optional[torch.Tensor], positions: Optional[torch.Tensor]) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] * scale + pos_table[positions[t], :] as float32 (the position row is
+    not scaled; ``pos_table`` None: no position row)."""
+    _need_cuda(out, table, ids, pos_table, positions)
+    _need_contiguous(out, table, ids, pos_table, positions)
+    if out.dtype != torch.float32 or ids.dtype != torch.int32:
+        raise KernelError("embedding writes float32 rows from int32 ids")
+    T, d = out.shape
+    if table.shape[1] != d or ids.numel() != T:
+        raise KernelError("embedding: shapes do not agree")
+    if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != d or positions is None
+                                  or positions.dtype != torch.int32 or positions.numel() != T):
+        raise KernelError("embedding: the position table has the embedding's dtype and width, positions are int32 [T]")
+    fn = _fn("elementwise", "pbe_embedding_pos",
+             [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(out), _ptr(table), _dtype_code(table), _ptr(ids), float(scale), _ptr(pos_table), _ptr(positions),
+              pos_table.shape[0] if pos_table is not None else 0, T, d, table.shape[0], _stream()), "embedding_pos")
+    return out
+
+
+def fold_pair(residual: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor],
+              delta_scale: float, first: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """[residual + delta_scale * (delta_a + delta_b) | first] as rows of twice the width in ``out_dtype``
+    (either delta may be None); residual and ``first`` are float32 [T, W]."""
+    _need_cuda(residual, delta_a, delta_b, first)
+    _need_contiguous(residual, delta_a, delta_b, first)
+    if residual.dtype != torch.float32 or first.dtype != torch.float32 or first.shape != residual.shape \
+            or residual.dim() != 2:
+        raise KernelError("fold_pair: the residual and the first rows are float32 [T, W]")
+    deltas = [x for x in (delta_a, delta_b) if x is not None]
+    for x in deltas:
+        if x.shape != residual.shape or x.dtype != deltas[0].dtype:
+            raise KernelError("fold_pair: the deltas have the residual's shape and one dtype")
+    T, d = residual.shape
+    out = torch.empty((T, 2 * d), dtype=out_dtype, device=residual.device)
+    fn = _fn("elementwise", "pbe_fold_pair", [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
+                                              c_int, c_int, c_void_p])
+    _check(fn(_ptr(residual), _ptr(delta_a), _ptr(delta_b), _dtype_code(deltas[0]) if deltas else F32,
+              float(delta_scale), _ptr(first), _ptr(out), _dtype_code(out), T, d, _stream()), "fold_pair")
+    return out
+
+
+GLU_ACTIVATIONS = {"silu": 0, "capped_swish": 1}
+
+
+def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", limit: float = 0.0,
+                     alpha: float = 1.0) -> torch.Tensor:
+    """out[r, c] = act(gate_up[r, c], gate_up[r, inter + c]).  "silu": silu(g) * u.  "capped_swish":
+    g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(alpha * g) * (u + 1)."""
+    if activation == "silu":
+        return silu_mul(gate_up, out)
+    _need_cuda(gate_up, out)
+    _need_contiguous(gate_up, out)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("gated_activation: shapes or dtypes do not agree")
+    fn = _fn("elementwise", "pbe_glu_act", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(_ptr(gate_up), _ptr(out), _dtype_code(out), rows, two_i // 2, GLU_ACTIVATIONS[activation], float(limit),
+              float(alpha), _stream()), "gated_activation")
+    return out
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
                 out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """residual += delta (float32, in place) and out = rmsnorm(residual) * gain.
@@ -1125,8 +1188,8 @@ def apply_penalty(logits, rows, tokens, penalties):
 # ------------------------------------------------------------------ two branches on one residual
 def add2_rmsnorm2(residual: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor],
                   gain1: torch.Tensor, gain2: Optional[torch.Tensor], eps: float,
-                  out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
-    """residual += (delta_a + delta_b) (float32, in place; either may be None), then the two RMS
+                  out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, delta_scale: float = 1.0):
+    """residual += delta_scale * (delta_a + delta_b) (float32, in place; either may be None), then the two RMS
     norms of the same row, out_i = gain_i * x * rsqrt(mean(x^2) + eps).  ``gain2`` None: one norm.
     With ``rows`` (int32 [n]) output row i is made from batch row rows[i] and the residual is left
     alone.  Returns (out1, out2 or None)."""
@@ -1151,10 +1214,10 @@ def add2_rmsnorm2(residual: torch.Tensor, delta_a: Optional[torch.Tensor], delta
     out2 = torch.empty((n, d), dtype=out_dtype, device=residual.device) if gain2 is not None else None
     fn = _fn("elementwise", "pbe_add2_rmsnorm2",
              [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-              c_float, c_void_p])
+              c_float, c_float, c_void_p])
     _check(fn(_ptr(residual), _ptr(delta_a), _ptr(delta_b), _dtype_code(deltas[0]) if deltas else F32, _ptr(gain1),
-              _ptr(gain2), _ptr(out1), _ptr(out2), _dtype_code(out1), _ptr(rows), n, d, float(eps), _stream()),
-           "add2_rmsnorm2")
+              _ptr(gain2), _ptr(out1), _ptr(out2), _dtype_code(out1), _ptr(rows), n, d, float(eps),
+              float(delta_scale), _stream()), "add2_rmsnorm2")
     return out1, out2
 
 
@@ -1362,6 +1425,111 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, sink: Optional[torch.
     return out
 
 
+# ------------------------------------------------------------------ masked attention (head norms, bias, sink, gate)
+MASKED_TILE_ROWS = 16     # packed rows (row x head of a key/value group) a block of the masked attention takes
+MASK_KINDS = {None: 0, "causal": 0, "window": 1, "chunk": 2}
+
+
+def head_norm_write(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bias: Optional[torch.Tensor],
+                    q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], slots: Optional[torch.Tensor],
+                    k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], num_heads: int,
+                    num_kv_heads: int, key_dim: int, value_dim: int, page_tokens: int, eps: float) -> torch.Tensor:
+    """From a fused projection [T, ld] (queries at column ``q_off``, keys at ``k_off``, values at
+    ``v_off``): ``bias`` (float32, indexed like the columns) added, an RMS norm over each query and
+    key head's ``key_dim`` elements with the gains ``q_gain`` / ``k_gain`` (float32 [key_dim], shared
+    by the heads; None: no norm), all in float32.  Returns the queries, float32 [T, H * D]; keys go to
+    ``k_pages`` [page, G, page_tokens, D] and values to ``v_pages`` [page, G, page_tokens, E] at
+    ``slots`` (None or a negative slot: nothing is written)."""
+    _need_cuda(proj, bias, q_gain, k_gain, slots, k_pages, v_pages)
+    _need_contiguous(bias, q_gain, k_gain, slots, k_pages, v_pages)
+    if proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("head_norm_write: the projection is [T, ld] with unit column stride")
+    T = proj.shape[0]
+    H, G, D, E = num_heads, num_kv_heads, key_dim, value_dim
+    if D > 256:
+        raise KernelError("head_norm_write: heads are at most 256 wide")
+    for g in (q_gain, k_gain):
+        if g is not None and (g.dtype != torch.float32 or g.numel() != D):
+            raise KernelError("head_norm_write: gains are float32 [key_dim]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() < max(q_off + H * D, k_off + G * D,
+                                                                              v_off + G * E)):
+        raise KernelError("head_norm_write: the bias is float32 and covers the projection's columns")
+    if k_pages is not None and (k_pages.dtype != proj.dtype or tuple(k_pages.shape[1:]) != (G, page_tokens, D)
+                                or v_pages is None or tuple(v_pages.shape[1:]) != (G, page_tokens, E)):
+        raise KernelError("head_norm_write: pages are [page, G, page_tokens, D] and [page, G, page_tokens, E]")
+    q = torch.empty((T, H * D), dtype=torch.float32, device=proj.device)
+    fn = _fn("masked_attention", "pbe_head_norm_write",
+             [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(bias), _ptr(q_gain), _ptr(k_gain),
+              _ptr(slots if k_pages is not None else None), _ptr(q), _ptr(k_pages), _ptr(v_pages), T, H, G, D, E,
+              int(page_tokens), float(eps), _dtype_code(proj), _stream()), "head_norm_write")
+    return q
+
+
+def masked_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, meta, num_heads: int,
+                     num_kv_heads: int, scale: float, mask: Optional[str], mask_size: Optional[int],
+                     page_tokens: int, bias: Optional[torch.Tensor] = None, unit_sink: bool = False,
+                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Softmax attention of every row over its request's pages.  ``q`` float32 [T, H * D]; pages
+    [page, G, page_tokens, D] and [page, G, page_tokens, E].  ``mask``: None / "causal" (every earlier
+    key), "window" (the last ``mask_size`` keys) or "chunk" (the earlier keys of the row's own chunk of
+    ``mask_size`` positions).  ``bias`` float32 [rows, H]: bias[min(distance, rows - 1), h] is added to
+    the scaled score.  ``unit_sink``: one more term e^0 in the denominator.  ``gate`` [T, >= H * E] (a
+    column slice in the pages' dtype): the output times its sigmoid.  ``meta``: the step's work list
+    for (group, H / G, ``MASKED_TILE_ROWS``, ``mask_size``).  Returns [T, H * E] in the pages' dtype."""
+    _need_cuda(q, k_pages, v_pages, bias, gate)
+    _need_contiguous(q, k_pages, v_pages, bias)
+    T = q.shape[0]
+    H, G = num_heads, num_kv_heads
+    D, E = k_pages.shape[-1], v_pages.shape[-1]
+    if q.dtype != torch.float32 or q.shape[1] != H * D or k_pages.dtype != v_pages.dtype:
+        raise KernelError("masked_attention: q is float32 [T, H * D]; the pages share a dtype")
+    if mask not in MASK_KINDS or (MASK_KINDS[mask] and not mask_size):
+        raise KernelError(f"masked_attention: unknown mask {mask!r}, or a mask without its size")
+    if bias is not None and (bias.dtype != torch.float32 or bias.dim() != 2 or bias.shape[1] != H):
+        raise KernelError("masked_attention: the bias is float32 [rows, H]")
+    if gate is not None and (gate.dtype != k_pages.dtype or gate.stride(1) != 1 or gate.shape[1] < H * E):
+        raise KernelError("masked_attention: the gate is a column slice [T, H * E] in the pages' dtype")
+    if E > 256:
+        raise KernelError("masked_attention: values are at most 256 wide")
+    out = torch.empty((T, H * E), dtype=k_pages.dtype, device=q.device)
+    part_o = part_ml = None
+    if meta.num_split_rows:
+        part_o, part_ml = meta.part_o, meta.part_ml
+        if part_o is None or tuple(part_o.shape) != (meta.num_split_rows, H, meta.max_splits, E):
+            part_o = torch.empty((meta.num_split_rows, H, meta.max_splits, E), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((meta.num_split_rows, H, meta.max_splits, 2), dtype=torch.float32, device=q.device)
+    ldg = 0
+    if gate is not None:
+        ldg = gate.stride(0) if T > 1 else max(gate.stride(0), H * E)
+    p = AttnParams(
+        q=q.data_ptr(), k_cache=k_pages.data_ptr(), v_cache=v_pages.data_ptr(), out=out.data_ptr(),
+        part_o=part_o.data_ptr() if part_o is not None else None,
+        part_ml=part_ml.data_ptr() if part_ml is not None else None,
+        q_start=meta.q_start.data_ptr(), q_len=meta.q_len.data_ptr(), seq_len=meta.seq_len.data_ptr(),
+        block_table=meta.block_table.data_ptr(), work=meta.work.data_ptr(),
+        tok_split_row=meta.tok_split_row.data_ptr(), bt_stride=int(meta.bt_stride),
+        num_heads=int(H), num_kv_heads=int(G), page_tokens=int(page_tokens),
+        window=int(mask_size or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
+        tile_rows=int(meta.tile_rows), scale=float(scale), kinds=0, num_pages=int(k_pages.shape[0]))
+    fn = _fn("masked_attention", "pbe_masked_attention",
+             [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int,
+              c_void_p])
+    _check(fn(ctypes.byref(p), int(D), int(E), _ptr(bias), bias.shape[0] if bias is not None else 0,
+              MASK_KINDS[mask], 1 if unit_sink else 0, _ptr(gate), int(ldg), int(meta.num_work),
+              _dtype_code(k_pages), _stream()), "masked_attention")
+    if meta.num_split_rows > 0:
+        mp = AttnMergeParams(part_o=part_o.data_ptr(), part_ml=part_ml.data_ptr(), out=out.data_ptr(),
+                             split_tokens=meta.split_tokens.data_ptr(), split_counts=meta.split_counts.data_ptr(),
+                             num_heads=int(H), head_dim=int(E), max_splits=int(meta.max_splits))
+        mfn = _fn("masked_attention", "pbe_masked_merge",
+                  [ctypes.POINTER(AttnMergeParams), c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(mfn(ctypes.byref(mp), 1 if unit_sink else 0, _ptr(gate), int(ldg), int(meta.num_split_rows),
+                   _dtype_code(k_pages), _stream()), "masked_merge")
+    return out
+
+
 # ------------------------------------------------------------------ routed experts
 def route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float):
     """(chosen int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E]: softmax
@@ -1384,10 +1552,12 @@ def route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float):
 
 
 def expert_rows(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                chosen: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum_k weights[t, k] * W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t)), e = chosen[t, k]:
+                chosen: torch.Tensor, weights: torch.Tensor, activation: str = "silu", limit: float = 0.0,
+                alpha: float = 1.0) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * W_down[e] act(W_gate[e] x_t, W_up[e] x_t), e = chosen[t, k]:
     a block per (row, chosen expert) streams that expert's matrices; for few rows.  ``w_gate_up``
-    [E, 2F, W]: an expert's gate rows followed by its up rows; ``w_down`` [E, W, F]."""
+    [E, 2F, W]: an expert's gate rows followed by its up rows; ``w_down`` [E, W, F].  ``activation``:
+    one of ``GLU_ACTIVATIONS`` (see ``gated_activation``)."""
     _need_cuda(x, w_gate_up, w_down, chosen, weights)
     _need_contiguous(x, w_gate_up, w_down, chosen, weights)
     T, W = x.shape
@@ -1403,11 +1573,13 @@ def expert_rows(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
     hidden = torch.empty((T * top, F), dtype=torch.float32, device=x.device)
     part = torch.empty((T, top, W), dtype=torch.float32, device=x.device)
     out = torch.empty((T, W), dtype=x.dtype, device=x.device)
-    fn = _fn("routed_experts", "pbe_expert_rows", [c_void_p] * 3 + [c_ll] + [c_void_p] * 6 + [c_int] * 5 + [c_void_p])
+    fn = _fn("routed_experts", "pbe_expert_rows", [c_void_p] * 3 + [c_ll] + [c_void_p] * 6 + [c_int] * 6 +
+             [c_float, c_float, c_void_p])
     global _launches
     up = c_void_p(w_gate_up.data_ptr() + F * W * w_gate_up.element_size())
     _check(fn(_ptr(x), _ptr(w_gate_up), up, 2 * F * W, _ptr(w_down), _ptr(chosen), _ptr(weights), _ptr(hidden),
-              _ptr(part), _ptr(out), _dtype_code(x), T, W, F, top, _stream()), "expert_rows")
+              _ptr(part), _ptr(out), _dtype_code(x), T, W, F, top, GLU_ACTIVATIONS[activation], float(limit),
+              float(alpha), _stream()), "expert_rows")
     _launches += 2
     return out
 

@@ -27,6 +27,8 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, dtype, self.device)
         self.embed = None
         self.lm_head = None
+        self.position_table = None
+        self.input_mixes: Dict[str, torch.Tensor] = {}
         # a cache layer's need is stated by the run step that writes it
         needs: List[object] = [None] * spec.num_cache_layers
         for step in spec.run_order:
@@ -38,6 +40,10 @@ class DecoderModel:
     def param_specs(self) -> List[ParamSpec]:
         s = self.spec
         specs = [ParamSpec(s.embedding_name, (s.vocab_size, s.hidden_size))]
+        if s.position_table_name is not None:
+            specs.append(ParamSpec(s.position_table_name, (s.max_position, s.hidden_size)))
+        for name in dict.fromkeys(st.input_mix for st in s.run_order if st.input_mix is not None):
+            specs.append(ParamSpec(name, (s.hidden_size, 2 * s.hidden_size)))
         for b in self.blocks:
             specs += b.param_specs()
         specs += self.final_norm.param_specs(s.final_norm_name)
@@ -51,6 +57,10 @@ class DecoderModel:
         s = self.spec
         tensors = dict(tensors)
         self.embed = tensors.pop(s.embedding_name).contiguous()
+        if s.position_table_name is not None:
+            self.position_table = tensors.pop(s.position_table_name).to(self.embed.dtype).contiguous()
+        for name in dict.fromkeys(st.input_mix for st in s.run_order if st.input_mix is not None):
+            self.input_mixes[name] = tensors.pop(name).contiguous()
         for b in self.blocks:
             b.load(tensors)
         self.final_norm.load(tensors, s.final_norm_name)
@@ -106,7 +116,9 @@ class DecoderModel:
             return None
         if self._native is None:
             descs = [native_exec.block_desc(b) for b in self.blocks]
-            ok = all(d is not None for d in descs) and all(st.writes_cache for st in self.spec.run_order)
+            ok = all(d is not None for d in descs) and all(st.writes_cache and st.input_mix is None
+                                                           for st in self.spec.run_order)
+            ok = ok and self.spec.embedding_scale == 1.0 and self.spec.position_table_name is None
             self._native = descs if ok else False
         return self._native or None
 
@@ -131,13 +143,37 @@ class DecoderModel:
             delta_in = delta_out
         return delta_in
 
+    def _mix_input(self, mix, residual, delta, first):
+        """x <- M [x ; e]: the pending branch outputs are folded into x while the operand is formed
+        (float32 sum, rounded once to the run dtype); the product's float32 result is the new
+        residual, in a buffer of its own (``first`` may be the old one)."""
+        from ..parts.norm import DeltaSum
+        if isinstance(delta, DeltaSum):
+            a, b, scale = delta.a, delta.b, delta.scale
+        else:
+            a, b, scale = delta, None, 1.0
+        if residual.dim() != 2:
+            raise ValueError("an input mix reads one residual stream")
+        operand = ops.fold_pair(residual, a, b, scale, first, self.dtype)
+        return ops.linear(operand, mix, None, out_dtype=torch.float32)
+
     def forward(self, ctx, storage) -> torch.Tensor:
         """Runs the step's rows through every run step; returns float32 logits at the
         wanted rows, [wanted, vocab]."""
         s = self.spec
         T = ctx.num_tokens
         residual = torch.empty((T, s.hidden_size), dtype=torch.float32, device=self.device)
-        ops.embedding(residual, self.embed, ctx.token_ids)
+        if s.embedding_scale != 1.0 or self.position_table is not None:
+            # a learned position row follows the token's place in the sequence
+            ops.embedding_positions(residual, self.embed, ctx.token_ids, s.embedding_scale, self.position_table,
+                                    ctx.positions)
+        else:
+            ops.embedding(residual, self.embed, ctx.token_ids)
+        first = None
+        if self.input_mixes:
+            # the embedding output, which input mixes read again: a copy unless the first run step
+            # replaces the residual at once (the norms add into the residual in place)
+            first = residual if s.run_order[0].input_mix is not None else residual.clone()
         if s.residual_streams > 1:
             # several residual streams, [T, S, W]: every one starts as the embedding
             residual = residual.unsqueeze(1).expand(T, s.residual_streams, s.hidden_size).contiguous()
@@ -151,6 +187,8 @@ class DecoderModel:
             for i, step in enumerate(s.run_order):
                 block = self.blocks[step.block]
                 cache = storage.layer(step.cache_layer, step.writes_cache)
+                if step.input_mix is not None:
+                    residual, delta = self._mix_input(self.input_mixes[step.input_mix], residual, delta, first), None
                 if traced:
                     with nvtx_range(f"layer.{i}"):
                         residual, delta = block.forward(residual, delta, ctx, cache)

@@ -11,6 +11,7 @@ from .pooled_attention import PooledWindowAttention
 from .parallel import ParallelMixer
 from .state_space import SelectiveStateSpace
 from .latent_attention import LatentAttention
+from .masked_attention import MaskedAttention
 from .streams import StreamBlock, StreamConnection
 
 __all__ = ["Block", "CacheTensor", "CompositeNeed", "FeedForward", "KVNeed", "Mixer", "Norm", "PagedNeed", "Part", "PositionEncoding",
@@ -18,4 +19,4 @@ __all__ = ["Block", "CacheTensor", "CompositeNeed", "FeedForward", "KVNeed", "Mi
            "build_block", "build_part", "register_part", "RMSNorm", "NoPositionEncoding", "RotaryEncoding",
            "GQAttention", "SwiGLU", "PreNormBlock", "LayerNorm", "PendingUpdate", "DecayLinearAttention",
            "PooledWindowAttention", "ParallelMixer", "StreamBlock", "StreamConnection", "DeltaSum", "ActivationMLP",
-           "RoutedExperts", "ParallelBlock", "SelectiveStateSpace", "LatentAttention"]
+           "RoutedExperts", "ParallelBlock", "SelectiveStateSpace", "LatentAttention", "MaskedAttention"]

@@ -15,11 +15,14 @@ class RMSNorm(Norm):
 
     The reference runs the add (add_kernel.cu:6-15) and the norm (rmsnorm_kernel.cu:9-41)
     as two launches and rounds the residual stream to the run dtype in between; here it is
-    one launch and the residual stream stays float32."""
+    one launch and the residual stream stays float32.
 
-    def __init__(self, size: int, eps: float, dtype, device, weight_name: str = "weight"):
+    ``one_plus``: the checkpoint stores the gain around zero, w = 1 + stored (formed once at load,
+    in float32)."""
+
+    def __init__(self, size: int, eps: float, dtype, device, weight_name: str = "weight", one_plus: bool = False):
         self.size, self.eps, self.dtype, self.device = int(size), float(eps), dtype, device
-        self.weight_name = weight_name
+        self.weight_name, self.one_plus = weight_name, bool(one_plus)
         self.gain = None
 
     def param_specs(self, prefix):
@@ -27,11 +30,13 @@ class RMSNorm(Norm):
 
     def load(self, tensors, prefix):
         self.gain = tensors[prefix + self.weight_name].to(torch.float32).contiguous()
+        if self.one_plus:
+            self.gain = (self.gain + 1.0).contiguous()
 
     def add_norm(self, residual, delta, rows=None, out_dtype=None):
         if isinstance(delta, DeltaSum):
             return ops.add2_rmsnorm2(residual, delta.a, delta.b, self.gain, None, self.eps,
-                                     out_dtype or self.dtype, rows)[0]
+                                     out_dtype or self.dtype, rows, delta_scale=delta.scale)[0]
         n = residual.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=out_dtype or self.dtype, device=residual.device)
         return ops.add_rmsnorm(residual, delta, self.gain, out, self.eps, rows)
@@ -41,8 +46,9 @@ class RMSNorm(Norm):
         in their gains only, so one launch and one root mean square serve both."""
         if other.size != self.size or other.eps != self.eps:
             raise ValueError("two norms of one row share its width and eps")
-        a, b = (delta.a, delta.b) if isinstance(delta, DeltaSum) else (delta, None)
-        return ops.add2_rmsnorm2(residual, a, b, self.gain, other.gain, self.eps, out_dtype or self.dtype)
+        a, b, scale = (delta.a, delta.b, delta.scale) if isinstance(delta, DeltaSum) else (delta, None, 1.0)
+        return ops.add2_rmsnorm2(residual, a, b, self.gain, other.gain, self.eps, out_dtype or self.dtype,
+                                 delta_scale=scale)
 
 
 class LayerNorm(Norm):
@@ -108,12 +114,12 @@ class LayerNorm(Norm):
 
 
 class DeltaSum:
-    """Two branch outputs of one layer that are not yet added to the residual: x' = x + (a + b).
-    The next norm's launch adds them."""
-    __slots__ = ("a", "b")
+    """Two branch outputs of one layer that are not yet added to the residual: x' = x + scale *
+    (a + b) (``b`` may be None).  The next norm's launch adds them."""
+    __slots__ = ("a", "b", "scale")
 
-    def __init__(self, a, b):
-        self.a, self.b = a, b
+    def __init__(self, a, b, scale: float = 1.0):
+        self.a, self.b, self.scale = a, b, float(scale)
 
 
 class PendingUpdate:

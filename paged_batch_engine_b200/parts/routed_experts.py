@@ -17,7 +17,9 @@ class RoutedExperts(FeedForward):
     experts form ``groups`` equal groups of neighbours, a group's score is its largest score and
     only experts of the ``keep`` best groups can be chosen (``groups`` 1: all can); the ``top``
     allowed experts with the largest scores are chosen; g = s / (sum of the chosen s + 1e-20) *
-    ``scale``.  Experts have no biases.
+    ``scale`` (with one group and scale 1 that is the softmax over the chosen logits alone).
+    Experts have no biases.  ``activation``: "silu" as above, or "capped_swish" with ``limit`` L and
+    ``alpha`` a: g <- min(W_gate x, L), u <- clamp(W_up x, -L, L), hidden = g sigmoid(a g) (u + 1).
 
     Steps of few rows stream each (row, chosen expert) pair's matrices; steps of many rows sort the
     rows by expert.  In bfloat16 every expert's run is padded to whole row tiles and one launch per
@@ -32,7 +34,8 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, dtype, device,
                  groups: int = 1, keep: Optional[int] = None, scale: float = 1.0, many_rows: int = 64,
-                 router_name: str = "router", expert_prefix: str = "e"):
+                 router_name: str = "router", expert_prefix: str = "e", activation: str = "silu",
+                 limit: float = 0.0, alpha: float = 1.0):
         keep = groups if keep is None else keep
         if num_experts % groups or not 1 <= keep <= groups or not 1 <= top <= keep * (num_experts // groups):
             raise ValueError("experts divide into equal groups, 1 <= keep <= groups, and the kept groups hold "
@@ -43,6 +46,11 @@ class RoutedExperts(FeedForward):
         self.num_experts, self.top, self.groups, self.keep = num_experts, top, groups, keep
         self.scale, self.many_rows = float(scale), int(many_rows)
         self.router_name, self.expert_prefix = router_name, expert_prefix
+        if activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"unknown expert activation {activation!r}; known: {', '.join(ops.GLU_ACTIVATIONS)}")
+        if activation == "capped_swish" and not limit > 0:
+            raise ValueError("the capped activation needs a positive limit")
+        self.activation, self.limit, self.alpha = activation, float(limit), float(alpha)
         self.dtype, self.device = dtype, device
         self.w_router = self.w_gate_up = self.w_down = None
 
@@ -72,11 +80,15 @@ class RoutedExperts(FeedForward):
         chosen, weights = ops.route(logits, self.top, self.groups, self.keep, self.scale)
         if x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16:
             if T < min(self.many_rows, self.MANY_ROWS_TILED):
-                return ops.expert_rows(x, self.w_gate_up, self.w_down, chosen, weights)
+                return self._rows(x, chosen, weights)
             return self._tiled(x, chosen, weights)
         if T < self.many_rows or getattr(ctx, "captured", False):
-            return ops.expert_rows(x, self.w_gate_up, self.w_down, chosen, weights)
+            return self._rows(x, chosen, weights)
         return self._sorted(x, chosen, weights)
+
+    def _rows(self, x, chosen, weights):
+        return ops.expert_rows(x, self.w_gate_up, self.w_down, chosen, weights, self.activation, self.limit,
+                               self.alpha)
 
     def _tiled(self, x, chosen, weights):
         """bfloat16: rows sorted by expert, every expert's run padded to whole row tiles, and one
@@ -89,7 +101,7 @@ class RoutedExperts(FeedForward):
         rows = ops.expert_gather(x, chosen, place, start, total_rows=max_tiles * ops.GROUP_TILE_ROWS)
         gu = ops.grouped_runs(rows, self.w_gate_up, tiles, self.dtype)
         hidden = torch.empty((rows.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
-        ops.silu_mul(gu, hidden)
+        ops.gated_activation(gu, hidden, self.activation, self.limit, self.alpha)
         out = ops.grouped_runs(hidden, self.w_down, tiles, self.dtype)
         return ops.expert_scatter(out, chosen, place, start, weights, T)
 
@@ -107,7 +119,7 @@ class RoutedExperts(FeedForward):
         for e, hi in enumerate(bounds):
             if hi > lo:
                 gu = ops.linear(rows[lo:hi], self.w_gate_up[e], None, out_dtype=self.dtype)
-                ops.silu_mul(gu, hidden[lo:hi])
+                ops.gated_activation(gu, hidden[lo:hi], self.activation, self.limit, self.alpha)
                 out[lo:hi] = ops.linear(hidden[lo:hi], self.w_down[e], None, out_dtype=self.dtype)
             lo = hi
         return ops.expert_scatter(out, chosen, place, start, weights, T)

@@ -26,6 +26,8 @@ class ParamSpec:
     shape: Tuple[int, ...]
     kind: str = "float"      # "float" or "int"
     optional: bool = False   # read if present, never reported as missing or unexpected
+    free_dims: Tuple[int, ...] = ()   # axes whose size the checkpoint decides (``shape`` holds the size random
+    #                                   weights are made with); the part reads the size from the tensor it is given
 
 
 class WeightsError(ValueError):
@@ -59,7 +61,9 @@ def check_names(expected: Sequence[ParamSpec], present: Dict[str, Tuple[str, Tup
         if n not in present:
             continue
         dt, shape = present[n]
-        if tuple(shape) != tuple(p.shape):
+        same = len(shape) == len(p.shape) and all(a == b or i in p.free_dims
+                                                  for i, (a, b) in enumerate(zip(shape, p.shape)))
+        if not same:
             wrong_shape.append((n, tuple(shape), tuple(p.shape)))
         ok = _INT if p.kind == "int" else _FLOAT
         if dt not in ok:
