@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """A design beside the engine's closest existing model at equal layer sizes (random weights).
 
-    python bench.py --design gebadra|bavetar [--steps K] [--warmup W] [--sizes 2048,4096]
+    python bench.py --design gebadra|bavetar|gusorax [--steps K] [--warmup W] [--sizes 2048,4096]
 
 For each size: prefill (one 2,048-token prompt in one step) and decode (batch 8 from 2,048-token
 contexts, the captured decode step) throughput of a few layers of the design and of a Qwen2 model
@@ -53,8 +53,30 @@ def bavetar_config(width: int) -> dict:
                 logit_softcap=30.0, layers=layers)
 
 
+def gusorax_config(width: int) -> dict:
+    """Four layer runs at the sizes of a real model of this kind: a windowed layer with a dense
+    feed-forward that runs twice (the loop), a chunked layer and a windowed layer with 32 experts of a
+    quarter of the dense width; heads of 128, an eighth as many key/value heads, a window of 1,024 and
+    chunks of 512, a bias table of 32 rows."""
+    heads, ff = width // 128, {2048: 5632, 4096: 11008}.get(width, width * 11 // 4)
+    kv = max(1, heads // 8)
+    win = dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=1024), bias_max=1024,
+               bias_rows=32)
+    chunk = dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=512))
+    dense = dict(kind="dense", ff=ff)
+    moe = dict(kind="moe", expert=dict(ff=ff // 4, limit=7.0), router=dict(experts=32, top=4))
+    layers = [dict(type="attention", mixer=win, mlp=dense), dict(type="attention_2", mixer=chunk, mlp=moe),
+              dict(type="attention", mixer=win, mlp=moe)]
+    return dict(architecture="Gusorax", width=width, vocab=32000, max_positions=8192, norm=dict(eps=1e-6),
+                embedding=dict(scale=float(width) ** 0.5), residual_mult=0.5, loop=dict(start=0, stop=1, times=2),
+                layers=layers)
+
+
 def qwen_config(width: int, design: str = "gebadra") -> dict:
-    if design == "bavetar":       # as many query heads; the usual eight times fewer key/value heads
+    if design == "gusorax":
+        g = gusorax_config(width)
+        heads, kv, ff = g["layers"][0]["mixer"]["heads"], g["layers"][0]["mixer"]["kv_heads"], g["layers"][0]["mlp"]["ff"]
+    elif design == "bavetar":       # as many query heads; the usual eight times fewer key/value heads
         heads, kv, ff = width // 128, max(1, width // 1024), bavetar_config(width)["layers"][0]["mlp"]["ff"]
     else:
         g = gebadra_config(width)
@@ -222,6 +244,45 @@ def rooflines_bavetar(width: int, pk: dict):
     return {"prefill": both(T, T * (T + 1) // 2, T), "decode": both(R, R * (C + 1), R * (C + 1))}
 
 
+def rooflines_gusorax(width: int, pk: dict):
+    """Algorithmic bytes and FLOPs of the compared kernels for the two workloads, per launch (the
+    attention's figures are those of the windowed layer, the wider of the two masks)."""
+    g = gusorax_config(width)
+    m = g["layers"][0]["mixer"]
+    H, G, D, E, W = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
+    ff = g["layers"][0]["mlp"]["ff"]
+    r = g["layers"][1]["mlp"]
+    NE, top, eff = r["router"]["experts"], r["router"]["top"], r["expert"]["ff"]
+    T, R, C = PROMPT, BATCH, PROMPT
+
+    def t_us(by, fl):
+        return max(by / (pk["hbm_gbs"] * 1e9), fl / (pk["bf16_tflops"] * 1e12)) * 1e6
+
+    def both(rows, keys_total, keys_read, qwen_total, qwen_read):
+        proj = (H * D + G * (D + E)) * 2
+        return {
+            # queries in, the visible keys and values read once, outputs; a score over D and a weighted sum over E
+            # for every (row, head, visible key)
+            "masked_attention": t_us(2 * rows * H * D + 2 * keys_read * G * (D + E) + 2 * rows * H * E,
+                                     2 * H * (D + E) * keys_total),
+            "head_norm_write": t_us(rows * proj + 2 * rows * H * D + 2 * rows * G * (D + E), 0),
+            "add2_rmsnorm2": t_us(rows * width * (2 * 4 + 2 * 2 + 2), 0),
+            "fold_pair": t_us(rows * width * (2 * 4 + 2 * 2 + 2 * 2), 0),
+            "embedding_positions": t_us(rows * width * (2 + 2 + 4), 0),
+            "gated_activation": t_us(rows * ff * 6, 0),
+            "expert_rows": t_us(2 * min(NE, rows * top) * 3 * eff * width, 6 * rows * top * eff * width),
+            "route": t_us(rows * NE * 4, 0),
+            "paged_attention": t_us(2 * (2 * rows * H * 128) + 2 * qwen_read * G * 2 * 128, 4 * H * 128 * qwen_total),
+            "attention_decode_fused": t_us(2 * qwen_read * G * 2 * 128, 4 * H * 128 * qwen_total),
+            "add_rmsnorm": t_us(rows * width * (2 * 4 + 2 + 2), 0),
+            "rope_kv_write": t_us(2 * rows * (H + 2 * G) * 128 * 2, 0),
+            "silu_mul": t_us(rows * ff * 6, 0),
+        }
+    keys_prefill = sum(min(t + 1, W) for t in range(T))
+    return {"prefill": both(T, keys_prefill, T, T * (T + 1) // 2, T),
+            "decode": both(R, R * min(C + 1, W), R * min(C + 1, W), R * (C + 1), R * (C + 1))}
+
+
 def rooflines(width: int, pk: dict):
     """Algorithmic bytes and FLOPs of the compared kernels for the two workloads, per launch."""
     g = gebadra_config(width)
@@ -259,8 +320,8 @@ def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
     from bench import ClockSampler, peaks
     from paged_batch_engine_b200.config import load_config
     from paged_batch_engine_b200.engine.runner import ModelRunner
-    if design not in ("gebadra", "bavetar"):
-        raise SystemExit(f"unknown design {design!r}; known: gebadra, bavetar")
+    if design not in ("gebadra", "bavetar", "gusorax"):
+        raise SystemExit(f"unknown design {design!r}; known: gebadra, bavetar, gusorax")
     os.environ["PBE_EXEC"] = "python"        # per-kernel times need every launch to come through ops
     pk = peaks()
     page = 16
@@ -273,12 +334,18 @@ def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
                "step_sizes", "gated_rms", "relu_squared", "route", "expert_rows", "expert_places", "expert_gather",
                "expert_scatter", "grouped_heads", "grouped_runs", "run_tiles"]
         theirs = theirs + ["silu_mul"]
-    design_config = bavetar_config if design == "bavetar" else gebadra_config
+    if design == "gusorax":
+        own = ["masked_attention", "head_norm_write", "add2_rmsnorm2", "fold_pair", "embedding_positions",
+               "gated_activation", "silu_mul", "route", "expert_rows", "expert_places", "expert_gather", "expert_scatter",
+               "grouped_runs", "run_tiles"]
+        theirs = theirs + ["silu_mul"]
+    design_config = {"bavetar": bavetar_config, "gusorax": gusorax_config}.get(design, gebadra_config)
+    roofs = {"bavetar": rooflines_bavetar, "gusorax": rooflines_gusorax}.get(design, rooflines)
     sampler = ClockSampler(0)
     sampler.active = True
     out = {}
     for width in sizes:
-        roof = rooflines_bavetar(width, pk) if design == "bavetar" else rooflines(width, pk)
+        roof = roofs(width, pk)
         row = {}
         for name, cfg, names in ((design, design_config(width), own), ("qwen2", qwen_config(width, design), theirs)):
             _, typed = load_config(cfg)

@@ -3,7 +3,7 @@
 //
 //   * mask: every earlier key, the last W keys (sliding window), or the earlier keys of the
 //     row's own chunk of C positions (chunks counted from position 0 of the sequence);
-//   * a bias per (distance, head) added to the scaled score: bias[min(i - j, rows - 1)][h], a table
+//   * a bias per (head, distance) added to the scaled score: bias[h][min(i - j, rows - 1)], a table
 //     the host expands from whatever rule the model has (buckets, slopes ...);
 //   * a unit sink: one more term e^0 in the softmax's denominator that carries no value;
 //   * a gate: the output of head h, element e, times sigmoid(gate[t][h * E + e]).
@@ -19,6 +19,7 @@
 // masked_merge: the key splits of a row put together, with the sink and the gate.
 #include "attention_params.cuh"
 #include "common.cuh"
+#include "masked_attention.cuh"
 #include "pdl.cuh"
 
 using namespace pbe;
@@ -92,36 +93,10 @@ __global__ void __launch_bounds__(128) head_norm_write_kernel(HeadNormParams p) 
 }
 
 // ------------------------------------------------------------------ masked_attention
-struct MaskedExtra {
-  const float* bias;         // [bias_rows, H] by distance, or null
-  int bias_rows;
-  int mask_kind;             // 0: all earlier keys, 1: the last `window` keys, 2: the row's chunk of `window` positions
-  int unit_sink;
-  const void* gate;          // [T, ldg] in the cache's dtype, column head * E + e, or null
-  int ldg;
-  int D, E;
-};
-
 constexpr int BM = 16;       // packed rows per block
 constexpr int BN = 32;       // keys per tile, one per lane
 constexpr int NWARPS = 4;
 constexpr int ROWS_PER_WARP = BM / NWARPS;
-
-__device__ __forceinline__ int first_visible(int pos, int mask_kind, int window) {
-  if (mask_kind == 1) return max(0, pos - window + 1);
-  if (mask_kind == 2) return (pos / window) * window;
-  return 0;
-}
-
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
-
-// the sink's term joins (m, l, acc scale): afterwards l includes e^(0 - m') and m' = max(m, 0)
-__device__ __forceinline__ void add_unit_sink(float& m, float& l, float& rescale) {
-  const float m2 = fmaxf(m, 0.f);
-  rescale = m == -INFINITY ? 0.f : expf(m - m2);
-  l = l * rescale + expf(-m2);
-  m = m2;
-}
 
 template <typename T, int EPL>
 __global__ void __launch_bounds__(NWARPS * 32) masked_attention_kernel(AttnParams p, MaskedExtra x) {
@@ -271,7 +246,7 @@ __global__ void __launch_bounds__(NWARPS * 32) masked_attention_kernel(AttnParam
       float sc = -INFINITY;
       if (visible) {
         sc = s[j] * p.scale;
-        if (x.bias) sc += __ldg(x.bias + (size_t)min(pos - key, x.bias_rows - 1) * H + row_head[j]);
+        if (x.bias) sc += __ldg(x.bias + (size_t)row_head[j] * x.bias_rows + min(pos - key, x.bias_rows - 1));
       }
       const float m_new = fmaxf(m_run[j], warp_max(sc));
       if (m_new == -INFINITY) continue;     // nothing visible so far

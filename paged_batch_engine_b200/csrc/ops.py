@@ -1474,7 +1474,7 @@ def masked_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     """Softmax attention of every row over its request's pages.  ``q`` float32 [T, H * D]; pages
     [page, G, page_tokens, D] and [page, G, page_tokens, E].  ``mask``: None / "causal" (every earlier
     key), "window" (the last ``mask_size`` keys) or "chunk" (the earlier keys of the row's own chunk of
-    ``mask_size`` positions).  ``bias`` float32 [rows, H]: bias[min(distance, rows - 1), h] is added to
+    ``mask_size`` positions).  ``bias`` float32 [H, rows]: bias[h, min(distance, rows - 1)] is added to
     the scaled score.  ``unit_sink``: one more term e^0 in the denominator.  ``gate`` [T, >= H * E] (a
     column slice in the pages' dtype): the output times its sigmoid.  ``meta``: the step's work list
     for (group, H / G, ``MASKED_TILE_ROWS``, ``mask_size``).  Returns [T, H * E] in the pages' dtype."""
@@ -1487,8 +1487,8 @@ def masked_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         raise KernelError("masked_attention: q is float32 [T, H * D]; the pages share a dtype")
     if mask not in MASK_KINDS or (MASK_KINDS[mask] and not mask_size):
         raise KernelError(f"masked_attention: unknown mask {mask!r}, or a mask without its size")
-    if bias is not None and (bias.dtype != torch.float32 or bias.dim() != 2 or bias.shape[1] != H):
-        raise KernelError("masked_attention: the bias is float32 [rows, H]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.dim() != 2 or bias.shape[0] != H):
+        raise KernelError("masked_attention: the bias is float32 [H, rows]")
     if gate is not None and (gate.dtype != k_pages.dtype or gate.stride(1) != 1 or gate.shape[1] < H * E):
         raise KernelError("masked_attention: the gate is a column slice [T, H * E] in the pages' dtype")
     if E > 256:
@@ -1516,7 +1516,7 @@ def masked_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     fn = _fn("masked_attention", "pbe_masked_attention",
              [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int,
               c_void_p])
-    _check(fn(ctypes.byref(p), int(D), int(E), _ptr(bias), bias.shape[0] if bias is not None else 0,
+    _check(fn(ctypes.byref(p), int(D), int(E), _ptr(bias), bias.shape[1] if bias is not None else 0,
               MASK_KINDS[mask], 1 if unit_sink else 0, _ptr(gate), int(ldg), int(meta.num_work),
               _dtype_code(k_pages), _stream()), "masked_attention")
     if meta.num_split_rows > 0:

@@ -144,7 +144,7 @@ class MaskedAttention(Mixer):
             # the table by distance: a row never reads a key further back than its window
             rows = torch.tensor([log_bucket(d, self.bias_rows, self.bias_far) for d in range(self.mask_size)],
                                 dtype=torch.long, device=rel.device)
-            self.bias_by_distance = rel[rows].contiguous()
+            self.bias_by_distance = rel[rows].t().contiguous()      # [H, mask_size]
 
     # ---- compute
     def forward(self, x, ctx, cache):
