@@ -1426,8 +1426,29 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, sink: Optional[torch.
 
 
 # ------------------------------------------------------------------ masked attention (head norms, bias, sink, gate)
-MASKED_TILE_ROWS = 16     # packed rows (row x head of a key/value group) a block of the masked attention takes
+MASKED_TILE_ROWS = 16     # packed rows (row x head of a key/value group) a block of the float32 masked attention takes
+MASKED_MMA_TILE_ROWS = 64  # and a block of the tensor-core one
 MASK_KINDS = {None: 0, "causal": 0, "window": 1, "chunk": 2}
+
+
+def masked_mma_applies(dtype: torch.dtype, key_dim: int, value_dim: int) -> bool:
+    """bfloat16 pages with head widths that are multiples of 16 run the masked attention on the tensor
+    cores; PBE_MASKED=plain keeps them on the float32-arithmetic kernel."""
+    return (dtype == torch.bfloat16 and key_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= key_dim <= 256
+            and 16 <= value_dim <= 256 and os.environ.get("PBE_MASKED", "").strip().lower() != "plain")
+
+
+def masked_tile_rows(dtype: torch.dtype, key_dim: int, value_dim: int) -> int:
+    """Packed rows a work item of ``masked_attention`` takes for these pages."""
+    return MASKED_MMA_TILE_ROWS if masked_mma_applies(dtype, key_dim, value_dim) else MASKED_TILE_ROWS
+
+
+def masked_libraries(dtype: torch.dtype, key_dim: int, value_dim: int):
+    """The (library, defines) pairs of the masked attention for these pages (for parallel builds)."""
+    jobs = [("masked_attention", None)]
+    if masked_mma_applies(dtype, key_dim, value_dim):
+        jobs.append(("masked_attention_mma", {"PBE_MA_D": int(key_dim), "PBE_MA_E": int(value_dim)}))
+    return jobs
 
 
 def head_norm_write(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bias: Optional[torch.Tensor],
@@ -1477,7 +1498,9 @@ def masked_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     ``mask_size`` positions).  ``bias`` float32 [H, rows]: bias[h, min(distance, rows - 1)] is added to
     the scaled score.  ``unit_sink``: one more term e^0 in the denominator.  ``gate`` [T, >= H * E] (a
     column slice in the pages' dtype): the output times its sigmoid.  ``meta``: the step's work list
-    for (group, H / G, ``MASKED_TILE_ROWS``, ``mask_size``).  Returns [T, H * E] in the pages' dtype."""
+    for (group, H / G, ``masked_tile_rows(dtype, D, E)``, ``mask_size``).  Returns [T, H * E] in the
+    pages' dtype.  Arithmetic is float32 throughout; on the tensor-core path the float32 queries and
+    softmax weights enter the products as two bfloat16 numbers each."""
     _need_cuda(q, k_pages, v_pages, bias, gate)
     _need_contiguous(q, k_pages, v_pages, bias)
     T = q.shape[0]
@@ -1513,12 +1536,19 @@ def masked_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         num_heads=int(H), num_kv_heads=int(G), page_tokens=int(page_tokens),
         window=int(mask_size or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
         tile_rows=int(meta.tile_rows), scale=float(scale), kinds=0, num_pages=int(k_pages.shape[0]))
-    fn = _fn("masked_attention", "pbe_masked_attention",
-             [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int,
-              c_void_p])
-    _check(fn(ctypes.byref(p), int(D), int(E), _ptr(bias), bias.shape[1] if bias is not None else 0,
-              MASK_KINDS[mask], 1 if unit_sink else 0, _ptr(gate), int(ldg), int(meta.num_work),
-              _dtype_code(k_pages), _stream()), "masked_attention")
+    if masked_mma_applies(k_pages.dtype, D, E):
+        fn = _fn("masked_attention_mma", "pbe_masked_attention_mma",
+                 [ctypes.POINTER(AttnParams), c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+                 {"PBE_MA_D": int(D), "PBE_MA_E": int(E)})
+        _check(fn(ctypes.byref(p), _ptr(bias), bias.shape[1] if bias is not None else 0, MASK_KINDS[mask],
+                  1 if unit_sink else 0, _ptr(gate), int(ldg), int(meta.num_work), _stream()), "masked_attention_mma")
+    else:
+        fn = _fn("masked_attention", "pbe_masked_attention",
+                 [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                  c_int, c_void_p])
+        _check(fn(ctypes.byref(p), int(D), int(E), _ptr(bias), bias.shape[1] if bias is not None else 0,
+                  MASK_KINDS[mask], 1 if unit_sink else 0, _ptr(gate), int(ldg), int(meta.num_work),
+                  _dtype_code(k_pages), _stream()), "masked_attention")
     if meta.num_split_rows > 0:
         mp = AttnMergeParams(part_o=part_o.data_ptr(), part_ml=part_ml.data_ptr(), out=out.data_ptr(),
                              split_tokens=meta.split_tokens.data_ptr(), split_counts=meta.split_counts.data_ptr(),

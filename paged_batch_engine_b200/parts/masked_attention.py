@@ -80,7 +80,7 @@ class MaskedAttention(Mixer):
             if mask != "window":
                 raise ValueError("a distance bias is tabulated over a window's distances")
         self.dtype, self.device = dtype, device
-        self.tile_rows = ops.MASKED_TILE_ROWS
+        self.tile_rows = ops.masked_tile_rows(dtype, key_dim, value_dim)
         self.w_in = self.b_in = self.w_o = self.b_o = self.q_gain = self.k_gain = self.bias_by_distance = None
 
     # ---- what it keeps
@@ -93,7 +93,7 @@ class MaskedAttention(Mixer):
         return [(self.num_heads // self.num_kv_heads, self.tile_rows, self.mask_size)]
 
     def kernel_libraries(self, dtype):
-        return [("masked_attention", None)] + ops.gemm_libraries(dtype)
+        return ops.masked_libraries(dtype, self.key_dim, self.value_dim) + ops.gemm_libraries(dtype)
 
     # ---- tensors
     def _columns(self):

@@ -248,3 +248,99 @@ BAV_LATENT_ONLY = dict(
     architecture="Bavetar", width=56, vocab=170, norm=dict(eps=1e-5), logit_scale=1.0, logit_softcap=12.0,
     layers=[dict(type="latent_attention", mixer=_lat(2, 12, 6, 6, 20, 26, 10, 3000.0, 0.2), mlp=None),
             dict(type="latent_attention", mixer=_lat(5, 8, 8, 8, 8, 16, 12, 3000.0, 0.3), mlp=_moe(16, 4, 2, 2, 1, 1.0))])
+
+
+# ---------------------------------------------------------------- Gusorax: tiny configurations
+def _win(heads, kv, dim, vdim, size, far, rows, scale):
+    return dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=scale, mask=dict(size=size), bias_max=far,
+                bias_rows=rows)
+
+
+def _chk(heads, kv, dim, vdim, size, scale):
+    return dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=scale, mask=dict(size=size))
+
+
+def _gmoe(ff, limit, experts, top):
+    return dict(kind="moe", expert=dict(ff=ff, limit=limit), router=dict(experts=experts, top=top))
+
+
+# a layer ahead of the loop and one after it, the loop runs two layers twice; three query heads on one
+# key/value head (a block's rows straddle tokens); head widths that are no multiples of 16 (the
+# float32-arithmetic kernel in bfloat16 too); windows and chunks that are no multiples of the page; a
+# layer without feed-forward; a bias table whose far end lies beyond the window
+GUS_A = dict(
+    architecture="Gusorax", width=64, vocab=300, max_positions=512, norm=dict(eps=1e-5), embedding=dict(scale=3.0),
+    residual_mult=0.5, loop=dict(start=1, stop=3, times=2),
+    layers=[
+        dict(type="attention", mixer=_win(3, 1, 24, 40, 21, 37.0, 12, 0.2), mlp=dict(kind="dense", ff=96)),
+        dict(type="attention_2", mixer=_chk(4, 2, 24, 20, 13, 0.25), mlp=_gmoe(48, 1.2, 6, 2)),
+        dict(type="attention", mixer=_win(6, 3, 8, 8, 50, 30.0, 8, 0.35), mlp=None),
+        dict(type="attention_2", mixer=_chk(2, 2, 40, 24, 30, 0.15), mlp=dict(kind="dense", ff=72)),
+    ])
+# no loop at all; as many key/value heads as query heads; head widths on the tensor-core path with
+# unequal key and value widths; a window of one token (a row sees itself only) and chunks of one; one
+# expert chosen; multiplier one
+GUS_B = dict(
+    architecture="Gusorax", width=96, vocab=211, max_positions=400, norm=dict(eps=1e-6), embedding=dict(scale=1.0),
+    residual_mult=1.0,
+    layers=[
+        dict(type="attention", mixer=_win(4, 4, 32, 16, 1, 9.0, 4, 0.3), mlp=_gmoe(40, 0.8, 5, 1)),
+        dict(type="attention_2", mixer=_chk(5, 5, 16, 48, 64, 0.3), mlp=dict(kind="dense", ff=64)),
+        dict(type="attention_2", mixer=_chk(2, 1, 32, 32, 1, 0.2), mlp=None),
+        dict(type="attention", mixer=_win(8, 2, 16, 32, 77, 300.0, 20, 0.25), mlp=_gmoe(24, 2.0, 4, 4)),
+    ])
+# the loop covers every layer and runs three times; sixteen query heads on two key/value heads; a
+# window longer than any test sequence; heads of 80 and 128 (unequal, tensor cores); every expert chosen
+GUS_C = dict(
+    architecture="Gusorax", width=128, vocab=257, max_positions=640, norm=dict(eps=3e-6), embedding=dict(scale=11.0),
+    residual_mult=0.25, loop=dict(start=0, stop=2, times=3),
+    layers=[
+        dict(type="attention", mixer=_win(16, 2, 80, 128, 600, 450.0, 16, 0.11), mlp=_gmoe(32, 3.0, 3, 3)),
+        dict(type="attention_2", mixer=_chk(8, 1, 48, 16, 40, 0.14), mlp=dict(kind="dense", ff=80)),
+    ])
+GUSORAX = {"A": (GUS_A, 41, 8), "B": (GUS_B, 42, 16), "C": (GUS_C, 43, 8)}     # config, seed, page tokens
+
+
+def make_gusorax_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str:
+    """A model folder with seeded random weights through the engine's random-weights mode, then
+    reshaped so that no mechanism is a near-identity: query and key projections large enough for
+    sharp softmaxes, bias tables that matter beside the scores, gains away from one, projection
+    biases and gates away from one half, decisive routers, experts that reach their limits."""
+    from paged_batch_engine_b200.config import load_config
+    from paged_batch_engine_b200.engine.runner import build_model
+    from paged_batch_engine_b200.weights import write_random_model
+    from safetensors.torch import load_file, save_file
+    _, typed = load_config(cfg)
+    model = build_model(typed, torch.float32, "cpu")
+    write_random_model(str(path), typed, model.param_specs(), seed, dtype)
+    f = os.path.join(str(path), "model.safetensors")
+    w = load_file(f)
+    g = torch.Generator().manual_seed(seed)
+    for k in list(w):
+        t = w[k].float()
+        leaf = k.split(".mix.")[-1] if ".mix." in k else k.split(".")[-1]
+        if leaf in ("q", "k") and t.dim() == 2:
+            t = t * 5.0
+        elif leaf in ("q.norm", "k.norm"):
+            t = 2.5 + 0.8 * torch.randn(t.shape, generator=g)
+        elif leaf == "rel":
+            t = torch.randn(t.shape, generator=g) * 2.0
+        elif leaf in ("v", "o", "g") and t.dim() == 2:
+            t = t * 4.0
+        elif leaf == "b" or k.endswith(".b"):
+            t = torch.randn(t.shape, generator=g) * 0.7
+        elif leaf in ("up", "down", "gate") and t.dim() == 2:
+            t = t * 4.5
+        elif leaf == "router":
+            t = t * 40.0
+        elif leaf in ("norm1", "norm"):
+            t = torch.randn(t.shape, generator=g) * 0.3
+        elif k == "pos":
+            t = torch.randn(t.shape, generator=g) * 0.5
+        elif k == "embed":
+            t = t * 20.0
+        elif k == "loop.in":
+            t = t * 3.0
+        w[k] = t.to(w[k].dtype)
+    save_file(w, f)
+    return str(path)
