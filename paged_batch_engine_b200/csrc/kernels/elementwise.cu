@@ -471,10 +471,49 @@ __global__ void glu_act_kernel(const T* __restrict__ in, T* __restrict__ out, in
   }
 }
 
+// The capped swish on bfloat16 rows, eight values a thread (16-byte loads and stores) as the silu
+// kernel above; float32 arithmetic with the fast exponential and reciprocal, the result is rounded
+// to bfloat16 anyway.
+__global__ void capped_swish_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                           int inter, int rows, float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunk = blockIdx.x * blockDim.x + threadIdx.x;
+  if (chunk * 8 >= inter) return;
+  for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+    const __nv_bfloat16* row = in + (size_t)r * 2 * inter;
+    const uint4 gq = *reinterpret_cast<const uint4*>(row + chunk * 8);
+    const uint4 uq = *reinterpret_cast<const uint4*>(row + inter + chunk * 8);
+    const unsigned gw[4] = {gq.x, gq.y, gq.z, gq.w}, uw[4] = {uq.x, uq.y, uq.z, uq.w};
+    unsigned yw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+      float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
+      g.x = fminf(g.x, limit);
+      g.y = fminf(g.y, limit);
+      u.x = fminf(fmaxf(u.x, -limit), limit);
+      u.y = fminf(fmaxf(u.y, -limit), limit);
+      const float s0 = __fdividef(1.0f, 1.0f + __expf(-alpha * g.x));
+      const float s1 = __fdividef(1.0f, 1.0f + __expf(-alpha * g.y));
+      const __nv_bfloat162 y = __floats2bfloat162_rn((g.x * s0) * (u.x + 1.0f), (g.y * s1) * (u.y + 1.0f));
+      yw[i] = *reinterpret_cast<const unsigned*>(&y);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)r * inter + chunk * 8) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
+  }
+}
+
 PBE_EXPORT int pbe_glu_act(const void* in, void* out, int dtype, int rows, int inter, int kind, float limit,
                            float alpha, cudaStream_t stream) {
   const size_t total = (size_t)rows * inter;
   if (total == 0) return 0;
+  if (kind == 1 && dtype == PBE_BF16 && (inter & 7) == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+    const int threads = 256, chunks = inter / 8;
+    dim3 grid((chunks + threads - 1) / threads, rows < 65535 ? rows : 65535);
+    launch_k(capped_swish_bf16x8_kernel, grid, threads, 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out,
+             inter, rows, limit, alpha);
+    return launch_status();
+  }
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == PBE_F32)

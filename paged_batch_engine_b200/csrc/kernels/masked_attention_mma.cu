@@ -68,25 +68,25 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* 
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
+// not volatile: a product is a function of its registers alone, so the compiler may order the
+// products of different accumulators between one another (two in a row on one accumulator wait for
+// each other)
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};\n"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// x = hi + lo + (an error of about 2^-17 |x|), both bfloat16
-__device__ __forceinline__ void split2(float x, bf16& hi, bf16& lo) {
-  hi = __float2bfloat16_rn(x);
-  lo = __float2bfloat16_rn(x - __bfloat162float(hi));
-}
-// two floats as a (hi, hi) and a (lo, lo) pair of bfloat16, the lower index in the lower half
+// x = hi + lo + (an error of about 2^-17 |x|), both bfloat16:
+// two floats as a (hi, hi) and a (lo, lo) pair of bfloat16, the lower index in the lower half; both
+// roundings of a pair in one conversion
 __device__ __forceinline__ void split_pair(float x, float y, unsigned& hi, unsigned& lo) {
-  bf16 xh, xl, yh, yl;
-  split2(x, xh, xl);
-  split2(y, yh, yl);
-  hi = (unsigned)__bfloat16_as_ushort(xh) | ((unsigned)__bfloat16_as_ushort(yh) << 16);
-  lo = (unsigned)__bfloat16_as_ushort(xl) | ((unsigned)__bfloat16_as_ushort(yl) << 16);
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+  hi = *reinterpret_cast<const unsigned*>(&h);
+  const float xh = __uint_as_float(hi << 16), yh = __uint_as_float(hi & 0xffff0000u);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(x - xh, y - yh);
+  lo = *reinterpret_cast<const unsigned*>(&l);
 }
 
 __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, MaskedExtra x) {
@@ -163,6 +163,15 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
   // the keys any row of this warp sees: tiles outside are skipped by the warp
   const int warp_lo = __reduce_min_sync(0xffffffffu, min(valid[0] ? lo[0] : INT_MAX, valid[1] ? lo[1] : INT_MAX));
   const int warp_hi = __reduce_max_sync(0xffffffffu, max(valid[0] ? hi[0] : -1, valid[1] ? hi[1] : -1));
+  // the keys EVERY row of this warp sees (empty when a row is idle): a tile inside needs no masking
+  const bool all_valid = __all_sync(0xffffffffu, valid[0] && valid[1]);
+  const int all_lo = all_valid ? __reduce_max_sync(0xffffffffu, max(lo[0], lo[1])) : INT_MAX;
+  const int all_hi = all_valid ? __reduce_min_sync(0xffffffffu, min(hi[0], hi[1])) : -1;
+  const float* bias_row[2] = {nullptr, nullptr};
+  if (x.bias) {
+    bias_row[0] = x.bias + (size_t)head[0] * x.bias_rows;
+    bias_row[1] = x.bias + (size_t)head[1] * x.bias_rows;
+  }
 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float O[ONT][4];
@@ -208,6 +217,22 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
       float S[SNT][4];
 #pragma unroll
       for (int nt = 0; nt < SNT; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
+      // the tile's biases are requested before the products, which hide their latency; a distance
+      // outside the table (a key no row sees) reads its nearest row and is masked below
+      float B[SNT][4];
+      if (x.bias) {
+        const int last = x.bias_rows - 1;
+        const int d0 = pos[0] - ts - 2 * t, d1 = pos[1] - ts - 2 * t;
+#pragma unroll
+        for (int nt = 0; nt < SNT; ++nt) {
+          if (keys_mode && (nt >> 1) != warp) continue;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int d = ((c >> 1) ? d1 : d0) - (nt * 8 + (c & 1));
+            B[nt][c] = __ldg(bias_row[c >> 1] + min(max(d, 0), last));
+          }
+        }
+      }
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
         unsigned ah[4], al[4];
@@ -220,27 +245,38 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
           unsigned kb[4];
           ldmatrix_x4(kb, Ks + ((n2 * 2 + (lane >> 4)) * 8 + (lane & 7)) * LDK + ks * 16 + ((lane >> 3) & 1) * 8);
           mma_bf16(S[2 * n2], ah, kb[0], kb[1]);
-          mma_bf16(S[2 * n2], al, kb[0], kb[1]);
           mma_bf16(S[2 * n2 + 1], ah, kb[2], kb[3]);
+          mma_bf16(S[2 * n2], al, kb[0], kb[1]);
           mma_bf16(S[2 * n2 + 1], al, kb[2], kb[3]);
         }
       }
       // scale, bias, mask; the tile's row maxima
       float mx[2] = {-INFINITY, -INFINITY};
+      if (!keys_mode && ts >= all_lo && ts + BN - 1 <= all_hi) {
+        // every row of the warp sees every key of the tile
 #pragma unroll
-      for (int nt = 0; nt < SNT; ++nt) {
-        const bool skip = keys_mode && (nt >> 1) != warp;
+        for (int nt = 0; nt < SNT; ++nt) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int i = c >> 1;
-          const int key = ts + nt * 8 + 2 * t + (c & 1);
-          float sc = -INFINITY;
-          if (!skip && key >= lo[i] && key <= hi[i]) {
-            sc = S[nt][c] * p.scale;
-            if (x.bias) sc += __ldg(x.bias + (size_t)head[i] * x.bias_rows + min(pos[i] - key, x.bias_rows - 1));
+          for (int c = 0; c < 4; ++c) {
+            const float sc = x.bias ? fmaf(S[nt][c], p.scale, B[nt][c]) : S[nt][c] * p.scale;
+            S[nt][c] = sc;
+            mx[c >> 1] = fmaxf(mx[c >> 1], sc);
           }
-          S[nt][c] = sc;
-          mx[i] = fmaxf(mx[i], sc);
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < SNT; ++nt) {
+          const bool skip = keys_mode && (nt >> 1) != warp;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int i = c >> 1;
+            const int key = ts + nt * 8 + 2 * t + (c & 1);
+            float sc = -INFINITY;
+            if (!skip && key >= lo[i] && key <= hi[i])
+              sc = x.bias ? fmaf(S[nt][c], p.scale, B[nt][c]) : S[nt][c] * p.scale;
+            S[nt][c] = sc;
+            mx[i] = fmaxf(mx[i], sc);
+          }
         }
       }
       float m_safe[2];
@@ -282,8 +318,8 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
           unsigned vb[4];
           ldmatrix_x4_trans(vb, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + o2 * 16 + (lane >> 4) * 8);
           mma_bf16(O[2 * o2], ph, vb[0], vb[1]);
-          mma_bf16(O[2 * o2], pl, vb[0], vb[1]);
           mma_bf16(O[2 * o2 + 1], ph, vb[2], vb[3]);
+          mma_bf16(O[2 * o2], pl, vb[0], vb[1]);
           mma_bf16(O[2 * o2 + 1], pl, vb[2], vb[3]);
         }
       }

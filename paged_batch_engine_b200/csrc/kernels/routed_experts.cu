@@ -68,7 +68,12 @@ __global__ void route_kernel(RouteParams p) {
   }
   sum = warp_sum(sum);
 #pragma unroll
-  for (int i = 0; i < MAX_PER_LANE; ++i) s[i] = s[i] / sum;
+  for (int i = 0; i < MAX_PER_LANE; ++i) {
+    // a row of logits that are not numbers (a padding row of a captured step, whose input nobody
+    // wrote) still chooses experts that exist: its scores count as 0 and the lowest indices win
+    const float v = s[i] / sum;
+    s[i] = v >= 0.f ? v : 0.f;
+  }
   // allowed[i]: may expert lane + 32 i still be chosen
   bool allowed[MAX_PER_LANE];
 #pragma unroll
