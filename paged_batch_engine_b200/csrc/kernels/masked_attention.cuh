@@ -14,6 +14,7 @@ struct MaskedExtra {
   const void* gate;          // [T, ldg] in the cache's dtype, column head * E + e, or null
   int ldg;
   int D, E;
+  int gate_pairs = 0;        // the gate's rows start on 4-byte boundaries: two values a load (tensor-core kernel)
 };
 
 __device__ __forceinline__ int first_visible(int pos, int mask_kind, int window) {

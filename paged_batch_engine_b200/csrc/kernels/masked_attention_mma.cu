@@ -130,7 +130,32 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
   const bf16* vc = (const bf16*)p.v_cache;
   const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
 
-  // queries: float32 from memory, split in two bfloat16 arrays
+  // the first key tile is requested before anything else
+  constexpr int TPR = NT / BN;          // threads that share a key's row when a tile is fetched
+  const int ld_j = tid / TPR, ld_part = tid - ld_j * TPR;
+  auto load_tile = [&](int stage, int ts) {
+    bf16* Ks = KVs + stage * STAGE_ELEMS;
+    bf16* Vs = Ks + BN * LDK;
+    const int key = ts + ld_j;
+    bool ok = key >= k_begin && key < k_end;
+    long long b = 0;
+    if (ok) {
+      const int page = bt[key / P];
+      ok = page >= 0;
+      if (ok) b = ((long long)page * KV + kvh) * P + key % P;
+    }
+    const bf16* ksrc = kc + b * D;
+    const bf16* vsrc = vc + b * E;
+    for (int c = ld_part; c < D / 8; c += TPR) cp_async16(Ks + ld_j * LDK + c * 8, ksrc + c * 8, ok);
+    for (int c = ld_part; c < E / 8; c += TPR) cp_async16(Vs + ld_j * LDV + c * 8, vsrc + c * 8, ok);
+  };
+
+  const int tile0 = (k_begin / BN) * BN;
+  if (tile0 < k_end) load_tile(0, tile0);
+  cp_async_commit();
+
+  // queries: float32 from memory, split in two bfloat16 arrays (the first key tile is on its way meanwhile)
+#pragma unroll 4
   for (int idx = tid; idx < BM * (D / 4); idx += NT) {
     const int i = idx / (D / 4), d = (idx - i * (D / 4)) * 4;
     const int pr = pr0 + i;
@@ -178,28 +203,6 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
 #pragma unroll
   for (int on = 0; on < ONT; ++on) O[on][0] = O[on][1] = O[on][2] = O[on][3] = 0.f;
 
-  constexpr int TPR = NT / BN;          // threads that share a key's row when a tile is fetched
-  const int ld_j = tid / TPR, ld_part = tid - ld_j * TPR;
-  auto load_tile = [&](int stage, int ts) {
-    bf16* Ks = KVs + stage * STAGE_ELEMS;
-    bf16* Vs = Ks + BN * LDK;
-    const int key = ts + ld_j;
-    bool ok = key >= k_begin && key < k_end;
-    long long b = 0;
-    if (ok) {
-      const int page = bt[key / P];
-      ok = page >= 0;
-      if (ok) b = ((long long)page * KV + kvh) * P + key % P;
-    }
-    const bf16* ksrc = kc + b * D;
-    const bf16* vsrc = vc + b * E;
-    for (int c = ld_part; c < D / 8; c += TPR) cp_async16(Ks + ld_j * LDK + c * 8, ksrc + c * 8, ok);
-    for (int c = ld_part; c < E / 8; c += TPR) cp_async16(Vs + ld_j * LDV + c * 8, vsrc + c * 8, ok);
-  };
-
-  const int tile0 = (k_begin / BN) * BN;
-  if (tile0 < k_end) load_tile(0, tile0);
-  cp_async_commit();
   int stage = 0;
   for (int ts = tile0; ts < k_end; ts += BN, stage ^= 1) {
     if (ts + BN < k_end) {
@@ -388,13 +391,28 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
       const float inv = l > 0.f ? rescale / l : 0.f;
       bf16* o = (bf16*)p.out + ((size_t)tok * H + head[i]) * E;
       const bf16* gt = x.gate ? (const bf16*)x.gate + (size_t)tok * x.ldg + head[i] * E : nullptr;
+      // the row's gate values are all requested before the first store (a store could alias them
+      // for all the compiler knows, and each request would wait behind it); pairs where the gate's
+      // rows start on 4-byte boundaries
+      float2 gv[ONT];
+      if (gt) {
+        if (x.gate_pairs) {
+#pragma unroll
+          for (int on = 0; on < ONT; ++on)
+            gv[on] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gt + on * 8 + 2 * t));
+        } else {
+#pragma unroll
+          for (int on = 0; on < ONT; ++on)
+            gv[on] = make_float2(__bfloat162float(gt[on * 8 + 2 * t]), __bfloat162float(gt[on * 8 + 2 * t + 1]));
+        }
+      }
 #pragma unroll
       for (int on = 0; on < ONT; ++on) {
         const int e = on * 8 + 2 * t;
         float y0 = O[on][2 * i] * inv, y1 = O[on][2 * i + 1] * inv;
         if (gt) {
-          y0 *= sigmoidf_(__bfloat162float(gt[e]));
-          y1 *= sigmoidf_(__bfloat162float(gt[e + 1]));
+          y0 *= sigmoidf_(gv[on].x);
+          y1 *= sigmoidf_(gv[on].y);
         }
         *reinterpret_cast<__nv_bfloat162*>(o + e) = __floats2bfloat162_rn(y0, y1);
       }
@@ -437,6 +455,7 @@ PBE_EXPORT int pbe_masked_attention_mma(const AttnParams* params, const float* b
     opted = true;
   }
   MaskedExtra x{bias, bias_rows, mask_kind, unit_sink, gate, ldg, D, E};
+  x.gate_pairs = gate != nullptr && ((uintptr_t)gate & 3) == 0 && (ldg & 1) == 0;
   launch_k(masked_attention_mma_kernel, dim3(num_work, p.num_kv_heads), NT, SMEM_BYTES, stream, p, x);
   return launch_status();
 }
