@@ -11,11 +11,14 @@
 // mma instructions and carries about 16 bits of the factor instead of 8.  Keys and values are the
 // bfloat16 numbers the pages hold.
 //
-// A block of four warps takes a tile of BM = 64 packed rows (row x query head of the key/value
+// A block of eight warps takes a tile of BM = 64 packed rows (row x query head of the key/value
 // group) and the keys of its split.  Two modes, by the rows the tile really has:
-//   rows mode (more than 16): warp w owns rows 16w .. 16w + 15 and visits every key of a key tile;
-//   keys mode (at most 16: decoded tokens): all warps own rows 0 .. 15 and warp w visits keys
-//   16w .. 16w + 15 of every key tile with statistics of its own; warp 0 merges the four at the end.
+//   rows mode (more than 16): warp w owns rows 16 (w & 3) .. 16 (w & 3) + 15 and visits half w >> 2 of
+//   every key tile with softmax statistics of its own; warp w + 4 hands its sums to warp w at the end
+//   (two warps a row group: sixteen warps a multiprocessor hide the chain ldmatrix -> mma -> softmax
+//   -> mma of a key tile, which eight did not);
+//   keys mode (at most 16: decoded tokens): all warps own rows 0 .. 15 and warp w < 4 visits keys
+//   16w .. 16w + 15 of every key tile; warp 0 merges the four at the end.
 //
 // Compile with -DPBE_MA_D=<key width> -DPBE_MA_E=<value width>, multiples of 16 up to 256.
 #include <cuda_bf16.h>
@@ -31,6 +34,12 @@ using namespace pbe;
 #error "PBE_MA_D and PBE_MA_E must be defined"
 #endif
 
+// blocks a multiprocessor the register budget aims at: two (sixteen warps) while the output
+// accumulator of a thread stays within 64 registers
+#ifndef PBE_MA_BLOCKS
+#define PBE_MA_BLOCKS ((PBE_MA_D <= 128 && PBE_MA_E <= 128) ? 2 : 1)
+#endif
+
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int D = PBE_MA_D, E = PBE_MA_E;
@@ -38,15 +47,16 @@ static_assert(D % 16 == 0 && E % 16 == 0 && D >= 16 && E >= 16 && D <= 256 && E 
               "head widths are multiples of 16, at most 256");
 constexpr int BM = 64;                         // packed rows per block
 constexpr int BN = (D + E > 256) ? 32 : 64;    // keys per tile
-constexpr int NT = 128;
+constexpr int NT = 256;                        // eight warps
 constexpr int LDQ = D + 8, LDK = D + 8, LDV = E + 8;   // shared row strides in elements (16-byte rows, no bank conflicts)
 constexpr int KSTEPS = D / 16;                 // k-steps of q . k
-constexpr int SNT = BN / 8;                    // 8-key score tiles per key tile
+constexpr int N2L = BN / 32;                   // 16-key score steps a warp takes of a key tile at most (half the tile)
+constexpr int SNT = 2 * N2L;                   // its 8-key score tiles
 constexpr int ONT = E / 8;                     // 8-wide output tiles
 constexpr int Q_ELEMS = BM * LDQ;              // one of the two query arrays
 constexpr int STAGE_ELEMS = BN * (LDK + LDV);
 constexpr size_t KV_BYTES = 2 * (size_t)STAGE_ELEMS * sizeof(bf16);
-constexpr size_t MERGE_BYTES = (size_t)3 * 16 * (E + 2) * sizeof(float);   // three warps' partial results
+constexpr size_t MERGE_BYTES = (size_t)4 * 16 * (E + 2) * sizeof(float);   // up to four warps' partial results
 constexpr size_t SMEM_BYTES = 2 * (size_t)Q_ELEMS * sizeof(bf16) + (KV_BYTES > MERGE_BYTES ? KV_BYTES : MERGE_BYTES);
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -89,7 +99,7 @@ __device__ __forceinline__ void split_pair(float x, float y, unsigned& hi, unsig
   lo = *reinterpret_cast<const unsigned*>(&l);
 }
 
-__global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, MaskedExtra x) {
+__global__ void __launch_bounds__(NT, PBE_MA_BLOCKS) masked_attention_mma_kernel(AttnParams p, MaskedExtra x) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qh = reinterpret_cast<bf16*>(smem_raw);     // [BM][LDQ] the queries' roundings
   bf16* Ql = Qh + Q_ELEMS;                          // and what the roundings left
@@ -172,7 +182,13 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
   }
 
   // this thread's two rows (g and g + 8 of the warp's sixteen): position, head, visible key range
-  const int row0 = keys_mode ? 0 : warp * 16;
+  // rows mode: warp w owns rows 16 (w & 3) .. and the half w >> 2 of every key tile; keys mode: all
+  // warps own rows 0 .. 15 and warp w < BN / 16 takes keys 16 w .. 16 w + 15 of every key tile
+  const int row0 = keys_mode ? 0 : (warp & 3) * 16;
+  const int koff = keys_mode ? warp * 16 : (warp >> 2) * (BN / 2);     // this warp's first key inside a tile
+  const int kwidth = keys_mode ? 16 : BN / 2;
+  const int n2_mine = keys_mode ? 1 : N2L;                              // its 16-key steps
+  const bool idle_warp = koff >= BN;                                    // keys mode: more warps than 16-key parts
   int pos[2], head[2], lo[2], hi[2];
   bool valid[2];
 #pragma unroll
@@ -213,22 +229,23 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
       cp_async_wait<0>();
     }
     __syncthreads();      // the tile has landed for every thread (and the queries are written, first time)
-    const bool mine = ts <= warp_hi && ts + BN > warp_lo;
+    const int tk = ts + koff;                 // this warp's first key of the tile
+    const bool mine = !idle_warp && tk <= warp_hi && tk + kwidth > warp_lo;
     if (mine) {
       const bf16* Ks = KVs + stage * STAGE_ELEMS;
       const bf16* Vs = Ks + BN * LDK;
       float S[SNT][4];
 #pragma unroll
       for (int nt = 0; nt < SNT; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
-      // the tile's biases are requested before the products, which hide their latency; a distance
-      // outside the table (a key no row sees) reads its nearest row and is masked below
+      // the biases are requested before the products, which hide their latency; a distance outside
+      // the table (a key no row sees) reads its nearest row and is masked below
       float B[SNT][4];
       if (x.bias) {
         const int last = x.bias_rows - 1;
-        const int d0 = pos[0] - ts - 2 * t, d1 = pos[1] - ts - 2 * t;
+        const int d0 = pos[0] - tk - 2 * t, d1 = pos[1] - tk - 2 * t;
 #pragma unroll
         for (int nt = 0; nt < SNT; ++nt) {
-          if (keys_mode && (nt >> 1) != warp) continue;
+          if ((nt >> 1) >= n2_mine) continue;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int d = ((c >> 1) ? d1 : d0) - (nt * 8 + (c & 1));
@@ -243,10 +260,10 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
         ldmatrix_x4(ah, Qh + qoff);
         ldmatrix_x4(al, Ql + qoff);
 #pragma unroll
-        for (int n2 = 0; n2 < SNT / 2; ++n2) {
-          if (keys_mode && n2 != warp) continue;
+        for (int n2 = 0; n2 < N2L; ++n2) {
+          if (n2 >= n2_mine) continue;
           unsigned kb[4];
-          ldmatrix_x4(kb, Ks + ((n2 * 2 + (lane >> 4)) * 8 + (lane & 7)) * LDK + ks * 16 + ((lane >> 3) & 1) * 8);
+          ldmatrix_x4(kb, Ks + (koff + (n2 * 2 + (lane >> 4)) * 8 + (lane & 7)) * LDK + ks * 16 + ((lane >> 3) & 1) * 8);
           mma_bf16(S[2 * n2], ah, kb[0], kb[1]);
           mma_bf16(S[2 * n2 + 1], ah, kb[2], kb[3]);
           mma_bf16(S[2 * n2], al, kb[0], kb[1]);
@@ -255,8 +272,8 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
       }
       // scale, bias, mask; the tile's row maxima
       float mx[2] = {-INFINITY, -INFINITY};
-      if (!keys_mode && ts >= all_lo && ts + BN - 1 <= all_hi) {
-        // every row of the warp sees every key of the tile
+      if (!keys_mode && tk >= all_lo && tk + kwidth - 1 <= all_hi) {
+        // every row of the warp sees every key of its part of the tile
 #pragma unroll
         for (int nt = 0; nt < SNT; ++nt) {
 #pragma unroll
@@ -269,11 +286,11 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
       } else {
 #pragma unroll
         for (int nt = 0; nt < SNT; ++nt) {
-          const bool skip = keys_mode && (nt >> 1) != warp;
+          const bool skip = (nt >> 1) >= n2_mine;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int i = c >> 1;
-            const int key = ts + nt * 8 + 2 * t + (c & 1);
+            const int key = tk + nt * 8 + 2 * t + (c & 1);
             float sc = -INFINITY;
             if (!skip && key >= lo[i] && key <= hi[i])
               sc = x.bias ? fmaf(S[nt][c], p.scale, B[nt][c]) : S[nt][c] * p.scale;
@@ -309,8 +326,8 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
       }
       // weights (two bfloat16 each) times values
 #pragma unroll
-      for (int kk = 0; kk < BN / 16; ++kk) {
-        if (keys_mode && kk != warp) continue;
+      for (int kk = 0; kk < N2L; ++kk) {
+        if (kk >= n2_mine) continue;
         unsigned ph[4], pl[4];
         split_pair(S[2 * kk][0], S[2 * kk][1], ph[0], pl[0]);
         split_pair(S[2 * kk][2], S[2 * kk][3], ph[1], pl[1]);
@@ -319,7 +336,7 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
 #pragma unroll
         for (int o2 = 0; o2 < ONT / 2; ++o2) {
           unsigned vb[4];
-          ldmatrix_x4_trans(vb, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + o2 * 16 + (lane >> 4) * 8);
+          ldmatrix_x4_trans(vb, Vs + (koff + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + o2 * 16 + (lane >> 4) * 8);
           mma_bf16(O[2 * o2], ph, vb[0], vb[1]);
           mma_bf16(O[2 * o2 + 1], ph, vb[2], vb[3]);
           mma_bf16(O[2 * o2], pl, vb[0], vb[1]);
@@ -336,13 +353,16 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
   }
-  if (keys_mode) {
-    // the four warps saw different keys of the same rows: warp 0 puts them together
+  {
+    // warps that saw different keys of the same rows are put together: in rows mode warp w + 4
+    // hands its sums to warp w (slot w), in keys mode warps 1 .. 3 hand theirs to warp 0 (slots 0 .. 2)
     float* M = reinterpret_cast<float*>(KVs);
-    if (warp > 0) {
+    const bool writer = !idle_warp && (keys_mode ? warp > 0 : warp >= 4);
+    const int slot = keys_mode ? warp - 1 : (warp & 3);
+    if (writer) {
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        float* dst = M + (size_t)((warp - 1) * 16 + g + 8 * i) * (E + 2);
+        float* dst = M + (size_t)(slot * 16 + g + 8 * i) * (E + 2);
 #pragma unroll
         for (int on = 0; on < ONT; ++on)
           *reinterpret_cast<float2*>(dst + on * 8 + 2 * t) = make_float2(O[on][2 * i], O[on][2 * i + 1]);
@@ -353,11 +373,13 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
       }
     }
     __syncthreads();
-    if (warp > 0) return;
+    if (writer || idle_warp) return;
+    const int first_slot = keys_mode ? 0 : warp;
+    const int n_slots = keys_mode ? min(4, BN / 16) - 1 : 1;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       float m = m_run[i];
-      for (int w = 0; w < 3; ++w) m = fmaxf(m, M[(size_t)(w * 16 + g + 8 * i) * (E + 2) + E]);
+      for (int w = 0; w < n_slots; ++w) m = fmaxf(m, M[(size_t)((first_slot + w) * 16 + g + 8 * i) * (E + 2) + E]);
       const float m_safe = m == -INFINITY ? 0.f : m;
       const float f0 = __expf(m_run[i] - m_safe);
       l_run[i] *= f0;
@@ -366,8 +388,8 @@ __global__ void __launch_bounds__(NT) masked_attention_mma_kernel(AttnParams p, 
         O[on][2 * i] *= f0;
         O[on][2 * i + 1] *= f0;
       }
-      for (int w = 0; w < 3; ++w) {
-        const float* src = M + (size_t)(w * 16 + g + 8 * i) * (E + 2);
+      for (int w = 0; w < n_slots; ++w) {
+        const float* src = M + (size_t)((first_slot + w) * 16 + g + 8 * i) * (E + 2);
         const float f = __expf(src[E] - m_safe);
         l_run[i] += src[E + 1] * f;
 #pragma unroll
