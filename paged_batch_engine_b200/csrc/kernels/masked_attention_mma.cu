@@ -143,17 +143,18 @@ __global__ void __launch_bounds__(NT, PBE_MA_BLOCKS) masked_attention_mma_kernel
   // the first key tile is requested before anything else
   constexpr int TPR = NT / BN;          // threads that share a key's row when a tile is fetched
   const int ld_j = tid / TPR, ld_part = tid - ld_j * TPR;
-  auto load_tile = [&](int stage, int ts) {
+  // the page of this thread's key in the tile at ts (-1: none); looked up a tile ahead of its use,
+  // so that the request for the tile does not wait for the block table
+  auto page_of = [&](int ts) -> int {
+    const int key = ts + ld_j;
+    return (ts < k_end && key >= k_begin && key < k_end) ? bt[key / P] : -1;
+  };
+  auto load_tile = [&](int stage, int ts, int page) {
     bf16* Ks = KVs + stage * STAGE_ELEMS;
     bf16* Vs = Ks + BN * LDK;
     const int key = ts + ld_j;
-    bool ok = key >= k_begin && key < k_end;
-    long long b = 0;
-    if (ok) {
-      const int page = bt[key / P];
-      ok = page >= 0;
-      if (ok) b = ((long long)page * KV + kvh) * P + key % P;
-    }
+    const bool ok = page >= 0;
+    const long long b = ok ? ((long long)page * KV + kvh) * P + key % P : 0;
     const bf16* ksrc = kc + b * D;
     const bf16* vsrc = vc + b * E;
     for (int c = ld_part; c < D / 8; c += TPR) cp_async16(Ks + ld_j * LDK + c * 8, ksrc + c * 8, ok);
@@ -161,8 +162,10 @@ __global__ void __launch_bounds__(NT, PBE_MA_BLOCKS) masked_attention_mma_kernel
   };
 
   const int tile0 = (k_begin / BN) * BN;
-  if (tile0 < k_end) load_tile(0, tile0);
+  int page_next = page_of(tile0);
+  if (tile0 < k_end) load_tile(0, tile0, page_next);
   cp_async_commit();
+  page_next = page_of(tile0 + BN);
 
   // queries: float32 from memory, split in two bfloat16 arrays (the first key tile is on its way meanwhile)
 #pragma unroll 4
@@ -222,8 +225,9 @@ __global__ void __launch_bounds__(NT, PBE_MA_BLOCKS) masked_attention_mma_kernel
   int stage = 0;
   for (int ts = tile0; ts < k_end; ts += BN, stage ^= 1) {
     if (ts + BN < k_end) {
-      load_tile(stage ^ 1, ts + BN);
+      load_tile(stage ^ 1, ts + BN, page_next);
       cp_async_commit();
+      page_next = page_of(ts + 2 * BN);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
