@@ -72,6 +72,10 @@ class ModelSpec:
     logit_softcap: Optional[float] = None   # c: logits <- c * tanh(logits / c), after the scale
     embedding_scale: float = 1.0   # the token's embedding row is multiplied by it
     position_table_name: Optional[str] = None   # a learned [max_position, W] table whose row p is added (unscaled)
+    embedding_norm: Optional[PartSpec] = None   # a norm applied to the gathered embedding row (tensor ``embedding_norm_name``)
+    embedding_norm_name: Optional[str] = None
+    depth_stack: Optional[str] = None   # blocks pass a ``DepthStack`` along: "mix" (every layer result is kept for
+    #                                     the layers' learned mixes over depth) or "plain" (only the latest)
 
     @property
     def num_cache_layers(self) -> int:

@@ -40,6 +40,8 @@ struct GroupGemmParams {
   int rot, rot_dims;
   const float* inv_freq;
   const int32_t* positions;
+  float rot_scale;           // cos and sin of the tail's rotation are both multiplied by it
+  int gate_each;             // the gate has a value per output column: gate[t * ldg + g * N + n]
 };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -196,12 +198,18 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(GroupGemmParams p) {
       if (r >= rows) continue;
       const int t = row0 + r;
       float gate = 1.f;
-      if (p.gate) gate = 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)t * p.ldg + g])));
+      if (p.gate && !p.gate_each) gate = 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)t * p.ldg + g])));
+      const __nv_bfloat16* gates = p.gate_each ? p.gate + (size_t)t * p.ldg + (size_t)g * p.N : nullptr;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int n = n0 + wn0 + j * 8 + q2;
-        if (n < p.N) out[(size_t)t * p.ldo + n] = from_float<TO>(acc[i][j][2 * hh] * gate);
-        if (n + 1 < p.N) out[(size_t)t * p.ldo + n + 1] = from_float<TO>(acc[i][j][2 * hh + 1] * gate);
+        float g0 = gate, g1 = gate;
+        if (gates) {
+          if (n < p.N) g0 = 1.0f / (1.0f + expf(-__bfloat162float(gates[n])));
+          if (n + 1 < p.N) g1 = 1.0f / (1.0f + expf(-__bfloat162float(gates[n + 1])));
+        }
+        if (n < p.N) out[(size_t)t * p.ldo + n] = from_float<TO>(acc[i][j][2 * hh] * g0);
+        if (n + 1 < p.N) out[(size_t)t * p.ldo + n + 1] = from_float<TO>(acc[i][j][2 * hh + 1] * g1);
       }
     }
   if (p.rot > 0 && blockIdx.z == 0) {
@@ -214,6 +222,8 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(GroupGemmParams p) {
       if (2 * pr + 1 < p.rot_dims) {
         float sn, cs;
         sincosf((float)p.positions[t] * p.inv_freq[pr], &sn, &cs);
+        sn *= p.rot_scale;
+        cs *= p.rot_scale;
         x = u * cs - v * sn;
         y = v * cs + u * sn;
       }
@@ -256,10 +266,11 @@ PBE_EXPORT int pbe_grouped_gemm(const void* a, int a_dtype, int lda, long long a
                                 int wk, int wn, void* out, int out_dtype, int ldo, long long out_group, int T, int K,
                                 int N, int groups, const int32_t* tiles, int num_tiles, const void* gate, int ldg,
                                 int rot, int rot_dims, const float* inv_freq, const int32_t* positions,
-                                cudaStream_t stream) {
+                                float rot_scale, int gate_each, cudaStream_t stream) {
   if (groups <= 0 || (tiles == nullptr && T <= 0) || (tiles != nullptr && num_tiles <= 0)) return 0;
   GroupGemmParams p{a, lda, a_group, (const __nv_bfloat16*)w, w_group, wk, wn, out, ldo, out_group, T, K, N, groups,
-                    tiles, (const __nv_bfloat16*)gate, ldg, rot, rot_dims, inv_freq, positions};
+                    tiles, (const __nv_bfloat16*)gate, ldg, rot, rot_dims, inv_freq, positions, rot_scale,
+                    gate_each};
   int nz = (N + GG_BN - 1) / GG_BN;
   if (nz == 0) nz = 1;
   dim3 grid = tiles ? dim3(num_tiles, 1, nz) : dim3((T + GG_BM - 1) / GG_BM, groups, nz);

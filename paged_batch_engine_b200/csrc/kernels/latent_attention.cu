@@ -34,6 +34,7 @@ struct PrepareParams {
   const float* c_gain;       // [rank]
   const float* inv_freq;     // [rot_dims / 2]
   int rot_dims;              // leading values of kr that are rotated, pairs (2i, 2i + 1)
+  float rot_scale;           // cos and sin are both multiplied by it (1: a pure rotation)
   const int32_t* positions;  // [T]
   const int32_t* slots;      // [T] page * page_tokens + offset, negative: nothing is written
   void* q_lat;               // [T, q_rank] normed query latent
@@ -77,6 +78,8 @@ __global__ void latent_prepare_kernel(PrepareParams p) {
     if (2 * i + 1 < p.rot_dims) {
       float sn, cs;
       sincosf(pos * p.inv_freq[i], &sn, &cs);
+      sn *= p.rot_scale;
+      cs *= p.rot_scale;
       a = u * cs - v * sn;
       b = v * cs + u * sn;
     }
@@ -101,9 +104,12 @@ struct HeadProductParams {
   int rot, rot_dims;
   const float* inv_freq;
   const int32_t* positions;
-  // optional gate: the result is multiplied by sigmoid(gate[t * ldg + h]); the gate has the weights' dtype
+  // optional gate: the result is multiplied by sigmoid(gate[t * ldg + h]), or (gate_each) by
+  // sigmoid(gate[t * ldg + h * N + n]), a gate per output value; the gate has the weights' dtype
   const void* gate;
   int ldg;
+  float rot_scale;           // cos and sin of the tail's rotation are both multiplied by it
+  int gate_each;
 };
 
 constexpr int HP_TM = 16, HP_TN = 64, HP_TK = 32;
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(256) head_product_kernel(HeadProductParams p) 
     if (t >= p.T || n >= p.N) continue;
     float v = acc[j];
     if (p.gate) {
-      const float g = to_float(((const TW*)p.gate)[(size_t)t * p.ldg + h]);
+      const float g = to_float(((const TW*)p.gate)[(size_t)t * p.ldg + (p.gate_each ? (size_t)h * p.N + n : (size_t)h)]);
       v *= 1.0f / (1.0f + expf(-g));
     }
     ((TO*)p.out)[(size_t)t * p.ldo + (size_t)h * p.ho + n] = from_float<TO>(v);
@@ -166,6 +172,8 @@ __global__ void __launch_bounds__(256) head_product_kernel(HeadProductParams p) 
       if (2 * pr + 1 < p.rot_dims) {
         float sn, cs;
         sincosf((float)p.positions[t] * p.inv_freq[pr], &sn, &cs);
+        sn *= p.rot_scale;
+        cs *= p.rot_scale;
         x = u * cs - v * sn;
         y = v * cs + u * sn;
       }
@@ -758,10 +766,11 @@ int dispatch_latent(const LatentAttnParams& lp, int num_work, cudaStream_t strea
 
 PBE_EXPORT int pbe_latent_prepare(const void* proj, int ld, int dtype, int q_off, int q_rank, int c_off, int rank,
                                   int r_off, int rot, const float* q_gain, const float* c_gain, const float* inv_freq,
-                                  int rot_dims, const int32_t* positions, const int32_t* slots, void* q_lat, void* cache,
-                                  float eps, int T, cudaStream_t stream) {
+                                  int rot_dims, float rot_scale, const int32_t* positions, const int32_t* slots,
+                                  void* q_lat, void* cache, float eps, int T, cudaStream_t stream) {
   if (T <= 0) return 0;
-  PrepareParams p{proj, ld, q_off, q_rank, c_off, rank, r_off, rot, q_gain, c_gain, inv_freq, rot_dims, positions,
+  PrepareParams p{proj, ld, q_off, q_rank, c_off, rank, r_off, rot, q_gain, c_gain, inv_freq, rot_dims, rot_scale,
+                  positions,
                   slots, q_lat, cache, eps};
   const int widest = q_rank > rank ? q_rank : rank;
   const int threads = widest >= 1024 ? 256 : 128;
@@ -774,9 +783,10 @@ PBE_EXPORT int pbe_latent_prepare(const void* proj, int ld, int dtype, int q_off
 PBE_EXPORT int pbe_head_product(const void* a, int lda, int ha, int a_dtype, const void* w, long long hw, int wk, int wn,
                                 int w_dtype, void* out, int ldo, int ho, int out_dtype, int T, int H, int K, int N,
                                 int rot, int rot_dims, const float* inv_freq, const int32_t* positions,
-                                const void* gate, int ldg, cudaStream_t stream) {
+                                const void* gate, int ldg, float rot_scale, int gate_each, cudaStream_t stream) {
   if (T <= 0 || H <= 0) return 0;
-  HeadProductParams p{a, lda, ha, w, hw, wk, wn, out, ldo, ho, T, H, K, N, rot, rot_dims, inv_freq, positions, gate, ldg};
+  HeadProductParams p{a, lda, ha, w, hw, wk, wn, out, ldo, ho, T, H, K, N, rot, rot_dims, inv_freq, positions, gate, ldg,
+                      rot_scale, gate_each};
   dim3 grid((T + HP_TM - 1) / HP_TM, H, (N + HP_TN - 1) / HP_TN);
   if (grid.z == 0) grid.z = 1;
   const int code = a_dtype * 4 + w_dtype * 2 + out_dtype;

@@ -9,8 +9,8 @@
 //   * a gate: the output of head h, element e, times sigmoid(gate[t][h * E + e]).
 //
 // head_norm_write: per token, the projection's bias, an RMS norm over each head's D query or key
-//   elements with one gain vector shared by the heads (float32 throughout), queries out in float32,
-//   keys and values into the pages.
+//   elements with one gain vector shared by the heads (float32 throughout), optionally a factor per
+//   query head (a learned temperature), queries out in float32, keys and values into the pages.
 // masked_attention: the float32-arithmetic kernel.  It reads the engine's attention work list
 //   (request, row tile, key split, splits): the rows of a request are packed with the query heads
 //   that share a key/value head, 16 packed rows a block, 32 keys a tile (a key a lane), online
@@ -33,6 +33,7 @@ struct HeadNormParams {
   const float* bias;         // indexed like the projection's columns, or null
   const float* q_gain;       // [D] or null: no norm
   const float* k_gain;       // [D] or null
+  const float* q_head_scale; // [H] or null: head h's normed query is multiplied by it (a temperature per head)
   const int32_t* slots;      // [T] page * page_tokens + offset; negative: nothing is written
   float* q_out;              // [T, H * D]
   void* k_pages;             // [page][G][page_tokens][D] or null
@@ -77,7 +78,8 @@ __global__ void __launch_bounds__(128) head_norm_write_kernel(HeadNormParams p) 
     for (int i = 0; i < HN_MAX; ++i) {
       const int d = lane + i * 32;
       if (d < D) {
-        const float y = gain ? (x[i] * sc) * gain[d] : x[i];
+        float y = gain ? (x[i] * sc) * gain[d] : x[i];
+        if (is_q && p.q_head_scale) y *= p.q_head_scale[head];
         if (is_q) p.q_out[((size_t)t * H + head) * D + d] = y;
         else ((T*)p.k_pages)[(((size_t)page * G + head) * PT + off) * D + d] = from_float<T>(y);
       }
@@ -381,12 +383,13 @@ PBE_EXPORT int pbe_masked_attention_tile_rows() { return BM; }
 PBE_EXPORT int pbe_masked_attention_key_tile() { return BN; }
 
 PBE_EXPORT int pbe_head_norm_write(const void* proj, int ld, int q_off, int k_off, int v_off, const float* bias,
-                                   const float* q_gain, const float* k_gain, const int32_t* slots, float* q_out,
+                                   const float* q_gain, const float* k_gain, const float* q_head_scale,
+                                   const int32_t* slots, float* q_out,
                                    void* k_pages, void* v_pages, int T, int H, int G, int D, int E, int page_tokens,
                                    float eps, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (D > 32 * HN_MAX || D < 1 || E < 1) return (int)cudaErrorInvalidValue;
-  HeadNormParams p{proj, ld, q_off, k_off, v_off, bias, q_gain, k_gain, slots, q_out, k_pages, v_pages,
+  HeadNormParams p{proj, ld, q_off, k_off, v_off, bias, q_gain, k_gain, q_head_scale, slots, q_out, k_pages, v_pages,
                    H, G, D, E, page_tokens, eps};
   if (dtype == PBE_F32) launch_k(head_norm_write_kernel<float>, T, 128, 0, stream, p);
   else launch_k(head_norm_write_kernel<__nv_bfloat16>, T, 128, 0, stream, p);

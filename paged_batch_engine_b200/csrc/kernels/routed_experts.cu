@@ -1,10 +1,13 @@
 // A feed-forward made of many small gated experts of which each token uses a few.
 //
-// route: from float32 router logits [T, E]: scores s = softmax over all experts; experts form
-// `groups` equal groups of neighbours, a group's score is its largest score, and only experts of
-// the `keep` best groups can be chosen (groups = 1: no restriction); the `top` allowed experts
-// with the largest scores are chosen (ties: the lower index); their weights are their scores over
-// the sum of the chosen scores (+ 1e-20), times `scale`.  One warp per token.
+// route: from float32 router logits [T, E]: scores s = softmax over all experts, or (score_kind 1)
+// sigmoid of each logit; the choice is made on c = s + correction (a learned vector, optional);
+// experts form `groups` equal groups of neighbours, a group's rank is its largest c or (group_rank
+// 2) the sum of its two largest, and only experts of the `keep` best groups can be chosen (groups =
+// 1: no restriction; a barred expert is out whatever its c, which may be negative); the `top`
+// allowed experts with the largest c are chosen (ties: the lower index); their weights are their
+// scores s, without the correction, over the sum of the chosen scores (+ 1e-20), times `scale`.
+// One warp per token.
 //
 // expert_rows: for few rows (decoded tokens).  Per (token, chosen expert) pair the expert's gate
 // and up rows are streamed against the token's input (blocks of 32 hidden units, a warp per unit,
@@ -30,6 +33,9 @@ struct RouteParams {
   float* weights;            // [T, top]
   int T, E, top, groups, keep;
   float scale;
+  int score_kind;            // 0: softmax over the experts, 1: sigmoid
+  const float* correction;   // [E] or null: added to the scores for the choice only
+  int group_rank;            // 1: a group's largest choice score, 2: the sum of its two largest
 };
 
 // the lane-distributed argmax of v (lane l holds experts l, l + 32, ...); ties go to the lower index
@@ -50,29 +56,44 @@ __global__ void route_kernel(RouteParams p) {
   if (t >= p.T) return;
   const int lane = threadIdx.x & 31, E = p.E;
   const float* z = p.logits + (size_t)t * E;
-  float s[MAX_PER_LANE];
-  float m = -INFINITY;
+  float s[MAX_PER_LANE];     // the scores
+  float c[MAX_PER_LANE];     // the choice scores
+  if (p.score_kind == 1) {
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      const float v = e < E ? 1.0f / (1.0f + expf(-z[e])) : 0.f;
+      s[i] = v >= 0.f ? v : 0.f;          // not a number (a padding row nobody wrote): counts as 0
+    }
+  } else {
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < E ? z[e] : -INFINITY;
+      m = fmaxf(m, s[i]);
+    }
+    m = warp_max(m);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < E ? expf(s[i] - m) : 0.f;
+      sum += s[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      // a row of logits that are not numbers (a padding row of a captured step, whose input nobody
+      // wrote) still chooses experts that exist: its scores count as 0 and the lowest indices win
+      const float v = s[i] / sum;
+      s[i] = v >= 0.f ? v : 0.f;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < MAX_PER_LANE; ++i) {
     const int e = lane + 32 * i;
-    s[i] = e < E ? z[e] : -INFINITY;
-    m = fmaxf(m, s[i]);
-  }
-  m = warp_max(m);
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAX_PER_LANE; ++i) {
-    const int e = lane + 32 * i;
-    s[i] = e < E ? expf(s[i] - m) : 0.f;
-    sum += s[i];
-  }
-  sum = warp_sum(sum);
-#pragma unroll
-  for (int i = 0; i < MAX_PER_LANE; ++i) {
-    // a row of logits that are not numbers (a padding row of a captured step, whose input nobody
-    // wrote) still chooses experts that exist: its scores count as 0 and the lowest indices win
-    const float v = s[i] / sum;
-    s[i] = v >= 0.f ? v : 0.f;
+    c[i] = s[i] + ((p.correction && e < E) ? p.correction[e] : 0.f);
   }
   // allowed[i]: may expert lane + 32 i still be chosen
   bool allowed[MAX_PER_LANE];
@@ -80,20 +101,51 @@ __global__ void route_kernel(RouteParams p) {
   for (int i = 0; i < MAX_PER_LANE; ++i) allowed[i] = lane + 32 * i < E;
   if (p.groups > 1 && p.keep < p.groups) {
     const int per = E / p.groups;
-    unsigned long long kept_lo = 0ull;          // bit g: group g is kept (groups <= 64)
-    for (int round = 0; round < p.keep; ++round) {
-      // the best group not kept yet: its score is the largest score of its experts
+    // rank of group g: in lane g % 32, slot g / 32 (groups <= 64)
+    float rank[2] = {-INFINITY, -INFINITY};
+    for (int g = 0; g < p.groups; ++g) {
       float best = -INFINITY;
       int at = 0x7fffffff;
 #pragma unroll
       for (int i = 0; i < MAX_PER_LANE; ++i) {
         const int e = lane + 32 * i;
-        if (e < E) {
-          const int g = e / per;
-          if (!((kept_lo >> g) & 1ull) && (s[i] > best || (s[i] == best && g < at))) { best = s[i]; at = g; }
+        if (e < E && e / per == g && (c[i] > best || (c[i] == best && e < at))) { best = c[i]; at = e; }
+      }
+      warp_argmax(best, at);
+      float value = best;
+      if (p.group_rank == 2 && per > 1) {
+        float second = -INFINITY;
+        int at2 = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i) {
+          const int e = lane + 32 * i;
+          if (e < E && e / per == g && e != at && (c[i] > second || (c[i] == second && e < at2))) {
+            second = c[i];
+            at2 = e;
+          }
+        }
+        warp_argmax(second, at2);
+        value = best + second;
+      }
+      if (lane == (g & 31)) rank[g >> 5] = value;
+    }
+    unsigned long long kept_lo = 0ull;          // bit g: group g is kept
+    for (int round = 0; round < p.keep; ++round) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int g = lane + 32 * j;
+        if (g < p.groups && !((kept_lo >> g) & 1ull) && (rank[j] > best || (rank[j] == best && g < at))) {
+          best = rank[j];
+          at = g;
         }
       }
       warp_argmax(best, at);
+      if (at >= p.groups) {                     // nothing compares (ranks that are not numbers): the lowest group left
+        at = 0;
+        while ((kept_lo >> at) & 1ull) ++at;
+      }
       kept_lo |= 1ull << at;
     }
 #pragma unroll
@@ -106,19 +158,28 @@ __global__ void route_kernel(RouteParams p) {
   int picked_e[MAX_TOP];
   float total = 0.f;
   for (int k = 0; k < p.top; ++k) {
-    float best = -INFINITY;
+    float best = -INFINITY, best_s = 0.f;
     int at = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) {
       const int e = lane + 32 * i;
-      if (allowed[i] && (s[i] > best || (s[i] == best && e < at))) { best = s[i]; at = e; }
+      if (allowed[i] && (at == 0x7fffffff || c[i] > best || (c[i] == best && e < at))) { best = c[i]; at = e; best_s = s[i]; }
     }
-    warp_argmax(best, at);
+    {   // the warp's best: the larger choice score, ties (and lanes with nothing) to the lower index
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+        const bool take = oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at));
+        if (take) { best = ob; at = oa; best_s = os; }
+      }
+    }
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i)
       if (lane + 32 * i == at) allowed[i] = false;
-    if (k < MAX_TOP) { picked_s[k] = best; picked_e[k] = at; }
-    total += best;
+    if (k < MAX_TOP) { picked_s[k] = best_s; picked_e[k] = at; }
+    total += best_s;
   }
   if (lane == 0) {
     const float inv = p.scale / (total + 1e-20f);
@@ -235,8 +296,10 @@ __global__ void __launch_bounds__(ER_WARPS * 32) expert_down_kernel(ExpertRowsPa
   }
 }
 
+// `addend` (optional, [T, W]): what every token gets besides its experts (a shared expert's output)
 template <typename T>
-__global__ void combine_kernel(const float* __restrict__ part, T* __restrict__ out, int top, int W, size_t total) {
+__global__ void combine_kernel(const float* __restrict__ part, const T* __restrict__ addend, T* __restrict__ out,
+                               int top, int W, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -244,6 +307,7 @@ __global__ void combine_kernel(const float* __restrict__ part, T* __restrict__ o
     const int c = (int)(i - t * W);
     float a = 0.f;
     for (int k = 0; k < top; ++k) a += part[(t * top + k) * W + c];
+    if (addend) a += to_float(addend[i]);
     out[i] = from_float<T>(a);
   }
 }
@@ -296,7 +360,8 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, const int32_t* __res
 template <typename T>
 __global__ void scatter_rows_kernel(const T* __restrict__ y, const int32_t* __restrict__ chosen,
                                     const int32_t* __restrict__ place, const int32_t* __restrict__ start,
-                                    const float* __restrict__ weights, T* __restrict__ out, int top, int W) {
+                                    const float* __restrict__ weights, const T* __restrict__ addend,
+                                    T* __restrict__ out, int top, int W) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float a = 0.f;
@@ -304,18 +369,21 @@ __global__ void scatter_rows_kernel(const T* __restrict__ y, const int32_t* __re
       const int pair = t * top + k;
       a += weights[pair] * to_float(y[(size_t)(start[chosen[pair]] + place[pair]) * W + i]);
     }
+    if (addend) a += to_float(addend[(size_t)t * W + i]);
     out[(size_t)t * W + i] = from_float<T>(a);
   }
 }
 }  // namespace
 
 PBE_EXPORT int pbe_route(const float* logits, int32_t* chosen, float* weights, int T, int E, int top, int groups,
-                         int keep, float scale, cudaStream_t stream) {
+                         int keep, float scale, int score_kind, const float* correction, int group_rank,
+                         cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E < 1 || E > 32 * MAX_PER_LANE || top < 1 || top > MAX_TOP || top > E || groups < 1 || groups > 64 ||
-      E % groups != 0 || keep < 1 || keep > groups || top > keep * (E / groups))
+      E % groups != 0 || keep < 1 || keep > groups || top > keep * (E / groups) || score_kind < 0 || score_kind > 1 ||
+      group_rank < 1 || group_rank > 2)
     return (int)cudaErrorInvalidValue;
-  RouteParams p{logits, chosen, weights, T, E, top, groups, keep, scale};
+  RouteParams p{logits, chosen, weights, T, E, top, groups, keep, scale, score_kind, correction, group_rank};
   launch_k(route_kernel, (T + 3) / 4, 128, 0, stream, p);
   return launch_status();
 }
@@ -323,7 +391,7 @@ PBE_EXPORT int pbe_route(const float* logits, int32_t* chosen, float* weights, i
 PBE_EXPORT int pbe_expert_rows(const void* x, const void* w_gate, const void* w_up, long long gu_stride,
                                const void* w_down, const int32_t* chosen, const float* weights, float* hidden,
                                float* part, void* out, int dtype, int T, int W, int F, int top, int act, float limit,
-                               float alpha, cudaStream_t stream) {
+                               float alpha, const void* addend, cudaStream_t stream) {
   if (T <= 0) return 0;
   ExpertRowsParams p{x, w_gate, w_up, gu_stride, w_down, chosen, weights, hidden, part, T, W, F, top, act, limit, alpha};
   const size_t smem1 = sizeof(float) * (size_t)W, smem2 = sizeof(float) * (size_t)F;
@@ -347,8 +415,12 @@ PBE_EXPORT int pbe_expert_rows(const void* x, const void* w_gate, const void* w_
   const size_t total = (size_t)T * W;
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  if (dtype == PBE_F32) launch_k(combine_kernel<float>, (int)blocks, 256, 0, stream, (const float*)part, (float*)out, top, W, total);
-  else launch_k(combine_kernel<__nv_bfloat16>, (int)blocks, 256, 0, stream, (const float*)part, (__nv_bfloat16*)out, top, W, total);
+  if (dtype == PBE_F32)
+    launch_k(combine_kernel<float>, (int)blocks, 256, 0, stream, (const float*)part, (const float*)addend, (float*)out,
+             top, W, total);
+  else
+    launch_k(combine_kernel<__nv_bfloat16>, (int)blocks, 256, 0, stream, (const float*)part,
+             (const __nv_bfloat16*)addend, (__nv_bfloat16*)out, top, W, total);
   return launch_status();
 }
 
@@ -372,12 +444,13 @@ PBE_EXPORT int pbe_expert_gather(const void* x, const int32_t* chosen, const int
 
 PBE_EXPORT int pbe_expert_scatter(const void* y, const int32_t* chosen, const int32_t* place, const int32_t* start,
                                   const float* weights, void* out, int dtype, int T, int top, int W,
-                                  cudaStream_t stream) {
+                                  const void* addend, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (dtype == PBE_F32)
-    scatter_rows_kernel<float><<<T, 128, 0, stream>>>((const float*)y, chosen, place, start, weights, (float*)out, top, W);
+    scatter_rows_kernel<float><<<T, 128, 0, stream>>>((const float*)y, chosen, place, start, weights,
+                                                     (const float*)addend, (float*)out, top, W);
   else
     scatter_rows_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)y, chosen, place, start, weights,
-                                                             (__nv_bfloat16*)out, top, W);
+                                                             (const __nv_bfloat16*)addend, (__nv_bfloat16*)out, top, W);
   return launch_status();
 }

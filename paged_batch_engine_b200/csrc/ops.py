@@ -1321,10 +1321,11 @@ def latent_tile_rows(num_heads: int) -> int:
 def latent_prepare(proj: torch.Tensor, q_off: int, q_rank: int, c_off: int, rank: int, r_off: int, rot: int,
                    q_gain: Optional[torch.Tensor], c_gain: torch.Tensor, inv_freq: Optional[torch.Tensor],
                    rot_dims: int, positions: torch.Tensor, slots: Optional[torch.Tensor],
-                   cache: Optional[torch.Tensor], eps: float) -> Optional[torch.Tensor]:
+                   cache: Optional[torch.Tensor], eps: float, rot_scale: float = 1.0) -> Optional[torch.Tensor]:
     """From the fused down projection [T, ld]: the RMS-normed query latent (returned, [T, q_rank];
     None when q_rank is 0) and, written into ``cache`` ([page, 1, page_tokens, rank + rot]) at
-    ``slots``: the RMS-normed latent c followed by the rotated shared key part."""
+    ``slots``: the RMS-normed latent c followed by the rotated shared key part (cos and sin of the
+    rotation both times ``rot_scale``)."""
     _need_cuda(proj, q_gain, c_gain, inv_freq, positions, slots, cache)
     _need_contiguous(proj, q_gain, c_gain, inv_freq, positions, slots, cache)
     T = proj.shape[0]
@@ -1340,9 +1341,9 @@ def latent_prepare(proj: torch.Tensor, q_off: int, q_rank: int, c_off: int, rank
     q_lat = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device) if q_rank else None
     fn = _fn("latent_attention", "pbe_latent_prepare",
              [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-              c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p])
+              c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p])
     _check(fn(_ptr(proj), proj.stride(0), _dtype_code(proj), q_off, q_rank, c_off, rank, r_off, rot, _ptr(q_gain),
-              _ptr(c_gain), _ptr(inv_freq), int(rot_dims), _ptr(positions), _ptr(slots), _ptr(q_lat), _ptr(cache),
+              _ptr(c_gain), _ptr(inv_freq), int(rot_dims), float(rot_scale), _ptr(positions), _ptr(slots), _ptr(q_lat), _ptr(cache),
               float(eps), T, _stream()), "latent_prepare")
     return q_lat
 
@@ -1350,23 +1351,27 @@ def latent_prepare(proj: torch.Tensor, q_off: int, q_rank: int, c_off: int, rank
 def head_product(a: torch.Tensor, lda: int, head_stride: int, K: int, w: torch.Tensor, w_head_stride: int,
                  wk: int, wn: int, N: int, out: torch.Tensor, ldo: int, out_head_stride: int, T: int, H: int,
                  rot: int = 0, rot_dims: int = 0, inv_freq: Optional[torch.Tensor] = None,
-                 positions: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 positions: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                 rot_scale: float = 1.0, gate_each: bool = False) -> torch.Tensor:
     """out[t, h, n] = sum_k a[t, h, k] * w[h][k * wk + n * wn] for n < N, per head, float32 sums in
     k order.  ``rot`` > 0: out[t, h, N : N + rot] = the rotation of a[t, h, K : K + rot] by the rows'
-    positions (pairs (2i, 2i + 1) of its first ``rot_dims`` values).  ``gate`` [T, >= H] (a column
-    slice in the weights' dtype): the result is multiplied by sigmoid(gate[t, h])."""
+    positions (pairs (2i, 2i + 1) of its first ``rot_dims`` values; cos and sin both times
+    ``rot_scale``).  ``gate`` [T, >= H] (a column slice in the weights' dtype): the result is
+    multiplied by sigmoid(gate[t, h]); with ``gate_each`` the gate is [T, >= H * N] and has a value
+    for every output, sigmoid(gate[t, h * N + n])."""
     _need_cuda(a, w, out, inv_freq, positions, gate)
     if gate is not None and (gate.stride(1) != 1 or gate.dtype != w.dtype):
         raise KernelError("head_product: the gate is a column slice in the weights' dtype")
     fn = _fn("latent_attention", "pbe_head_product",
              [c_void_p, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p])
     ldg = 0
     if gate is not None:
-        ldg = gate.stride(0) if T > 1 else max(gate.stride(0), H)
+        ldg = gate.stride(0) if T > 1 else max(gate.stride(0), H * (N if gate_each else 1))
     _check(fn(_ptr(a), int(lda), int(head_stride), _dtype_code(a), _ptr(w), int(w_head_stride), int(wk), int(wn),
               _dtype_code(w), _ptr(out), int(ldo), int(out_head_stride), _dtype_code(out), int(T), int(H), int(K),
-              int(N), int(rot), int(rot_dims), _ptr(inv_freq), _ptr(positions), _ptr(gate), int(ldg), _stream()),
+              int(N), int(rot), int(rot_dims), _ptr(inv_freq), _ptr(positions), _ptr(gate), int(ldg),
+              float(rot_scale), 1 if gate_each else 0, _stream()),
            "head_product")
     return out
 
@@ -1454,15 +1459,19 @@ def masked_libraries(dtype: torch.dtype, key_dim: int, value_dim: int):
 def head_norm_write(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bias: Optional[torch.Tensor],
                     q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], slots: Optional[torch.Tensor],
                     k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], num_heads: int,
-                    num_kv_heads: int, key_dim: int, value_dim: int, page_tokens: int, eps: float) -> torch.Tensor:
+                    num_kv_heads: int, key_dim: int, value_dim: int, page_tokens: int, eps: float,
+                    q_head_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """From a fused projection [T, ld] (queries at column ``q_off``, keys at ``k_off``, values at
     ``v_off``): ``bias`` (float32, indexed like the columns) added, an RMS norm over each query and
     key head's ``key_dim`` elements with the gains ``q_gain`` / ``k_gain`` (float32 [key_dim], shared
-    by the heads; None: no norm), all in float32.  Returns the queries, float32 [T, H * D]; keys go to
+    by the heads; None: no norm), all in float32; ``q_head_scale`` (float32 [H]) multiplies head h's
+    normed query (a temperature per head).  Returns the queries, float32 [T, H * D]; keys go to
     ``k_pages`` [page, G, page_tokens, D] and values to ``v_pages`` [page, G, page_tokens, E] at
     ``slots`` (None or a negative slot: nothing is written)."""
-    _need_cuda(proj, bias, q_gain, k_gain, slots, k_pages, v_pages)
-    _need_contiguous(bias, q_gain, k_gain, slots, k_pages, v_pages)
+    _need_cuda(proj, bias, q_gain, k_gain, slots, k_pages, v_pages, q_head_scale)
+    _need_contiguous(bias, q_gain, k_gain, slots, k_pages, v_pages, q_head_scale)
+    if q_head_scale is not None and (q_head_scale.dtype != torch.float32 or q_head_scale.numel() != num_heads):
+        raise KernelError("head_norm_write: the heads' factors are float32 [H]")
     if proj.dim() != 2 or proj.stride(1) != 1:
         raise KernelError("head_norm_write: the projection is [T, ld] with unit column stride")
     T = proj.shape[0]
@@ -1481,9 +1490,9 @@ def head_norm_write(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bias
     q = torch.empty((T, H * D), dtype=torch.float32, device=proj.device)
     fn = _fn("masked_attention", "pbe_head_norm_write",
              [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     _check(fn(_ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(bias), _ptr(q_gain), _ptr(k_gain),
-              _ptr(slots if k_pages is not None else None), _ptr(q), _ptr(k_pages), _ptr(v_pages), T, H, G, D, E,
+              _ptr(q_head_scale), _ptr(slots if k_pages is not None else None), _ptr(q), _ptr(k_pages), _ptr(v_pages), T, H, G, D, E,
               int(page_tokens), float(eps), _dtype_code(proj), _stream()), "head_norm_write")
     return q
 
@@ -1561,12 +1570,24 @@ def masked_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
 
 
 # ------------------------------------------------------------------ routed experts
-def route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float):
-    """(chosen int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E]: softmax
-    scores, experts outside the ``keep`` best of ``groups`` neighbouring groups barred, the top
-    scores chosen, weights = score / (sum of the chosen + 1e-20) * scale."""
-    _need_cuda(logits)
-    _need_contiguous(logits)
+ROUTER_SCORES = {"softmax": 0, "sigmoid": 1}
+GROUP_RANKS = {"max": 1, "top2_sum": 2}
+
+
+def route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float, score: str = "softmax",
+          correction: Optional[torch.Tensor] = None, group_rank: str = "max"):
+    """(chosen int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E]: scores
+    by ``score`` ("softmax" over the experts or "sigmoid" of each logit); the choice is made on the
+    scores plus ``correction`` (float32 [E], optional): experts outside the ``keep`` best of
+    ``groups`` neighbouring groups barred (a group ranks by ``group_rank``: its "max" or its
+    "top2_sum"), the top ones chosen; weights = score (uncorrected) / (sum of the chosen + 1e-20) *
+    scale."""
+    _need_cuda(logits, correction)
+    _need_contiguous(logits, correction)
+    if score not in ROUTER_SCORES or group_rank not in GROUP_RANKS:
+        raise KernelError(f"route: scores are one of {sorted(ROUTER_SCORES)}, group ranks one of {sorted(GROUP_RANKS)}")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != logits.shape[1]):
+        raise KernelError("route: the correction is float32 [E]")
     T, E = logits.shape
     if logits.dtype != torch.float32:
         raise KernelError("route: router logits are float32")
@@ -1575,16 +1596,16 @@ def route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float):
     chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     fn = _fn("routed_experts", "pbe_route", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                            c_void_p])
+                                            c_int, c_void_p, c_int, c_void_p])
     _check(fn(_ptr(logits), _ptr(chosen), _ptr(weights), T, E, int(top), int(groups), int(keep), float(scale),
-              _stream()), "route")
+              ROUTER_SCORES[score], _ptr(correction), GROUP_RANKS[group_rank], _stream()), "route")
     return chosen, weights
 
 
 def expert_rows(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
                 chosen: torch.Tensor, weights: torch.Tensor, activation: str = "silu", limit: float = 0.0,
-                alpha: float = 1.0) -> torch.Tensor:
-    """out[t] = sum_k weights[t, k] * W_down[e] act(W_gate[e] x_t, W_up[e] x_t), e = chosen[t, k]:
+                alpha: float = 1.0, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = (addend[t], optional) + sum_k weights[t, k] * W_down[e] act(W_gate[e] x_t, W_up[e] x_t), e = chosen[t, k]:
     a block per (row, chosen expert) streams that expert's matrices; for few rows.  ``w_gate_up``
     [E, 2F, W]: an expert's gate rows followed by its up rows; ``w_down`` [E, W, F].  ``activation``:
     one of ``GLU_ACTIVATIONS`` (see ``gated_activation``)."""
@@ -1603,13 +1624,16 @@ def expert_rows(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
     hidden = torch.empty((T * top, F), dtype=torch.float32, device=x.device)
     part = torch.empty((T, top, W), dtype=torch.float32, device=x.device)
     out = torch.empty((T, W), dtype=x.dtype, device=x.device)
+    if addend is not None and (addend.shape != x.shape or addend.dtype != x.dtype or not addend.is_cuda
+                               or not addend.is_contiguous()):
+        raise KernelError("expert_rows: the addend has the rows' shape and dtype")
     fn = _fn("routed_experts", "pbe_expert_rows", [c_void_p] * 3 + [c_ll] + [c_void_p] * 6 + [c_int] * 6 +
-             [c_float, c_float, c_void_p])
+             [c_float, c_float, c_void_p, c_void_p])
     global _launches
     up = c_void_p(w_gate_up.data_ptr() + F * W * w_gate_up.element_size())
     _check(fn(_ptr(x), _ptr(w_gate_up), up, 2 * F * W, _ptr(w_down), _ptr(chosen), _ptr(weights), _ptr(hidden),
               _ptr(part), _ptr(out), _dtype_code(x), T, W, F, top, GLU_ACTIVATIONS[activation], float(limit),
-              float(alpha), _stream()), "expert_rows")
+              float(alpha), _ptr(addend), _stream()), "expert_rows")
     _launches += 2
     return out
 
@@ -1644,16 +1668,19 @@ def expert_gather(x: torch.Tensor, chosen: torch.Tensor, place: torch.Tensor, st
 
 
 def expert_scatter(y: torch.Tensor, chosen: torch.Tensor, place: torch.Tensor, start: torch.Tensor,
-                   weights: torch.Tensor, T: int) -> torch.Tensor:
-    """out[t] = sum_k weights[t, k] * y[start[e] + place[(t, k)]], e = chosen[t, k], in k order."""
-    _need_cuda(y, chosen, place, start, weights)
-    _need_contiguous(y, chosen, place, start, weights)
+                   weights: torch.Tensor, T: int, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * y[start[e] + place[(t, k)]], e = chosen[t, k], in k order, plus
+    ``addend`` [T, W] (optional, y's dtype)."""
+    _need_cuda(y, chosen, place, start, weights, addend)
+    _need_contiguous(y, chosen, place, start, weights, addend)
+    if addend is not None and (tuple(addend.shape) != (T, y.shape[1]) or addend.dtype != y.dtype):
+        raise KernelError("expert_scatter: the addend is [T, W] in the rows' dtype")
     W = y.shape[1]
     top = chosen.shape[1]
     out = torch.empty((T, W), dtype=y.dtype, device=y.device)
-    fn = _fn("routed_experts", "pbe_expert_scatter", [c_void_p] * 6 + [c_int] * 4 + [c_void_p])
+    fn = _fn("routed_experts", "pbe_expert_scatter", [c_void_p] * 6 + [c_int] * 4 + [c_void_p, c_void_p])
     _check(fn(_ptr(y), _ptr(chosen), _ptr(place), _ptr(start), _ptr(weights), _ptr(out), _dtype_code(y), T, top, W,
-              _stream()), "expert_scatter")
+              _ptr(addend), _stream()), "expert_scatter")
     return out
 
 
@@ -1662,31 +1689,32 @@ GROUP_TILE_ROWS = 64     # rows of a tile of the grouped product (runs of rows a
 
 
 def _grouped(a, lda, a_group, w, w_group, wk, wn, out, ldo, out_group, T, K, N, groups, tiles, num_tiles,
-             gate=None, rot=0, rot_dims=0, inv_freq=None, positions=None):
+             gate=None, rot=0, rot_dims=0, inv_freq=None, positions=None, rot_scale=1.0, gate_each=False):
     _need_cuda(a, w, out, tiles, gate, inv_freq, positions)
     if w.dtype != torch.bfloat16 or (gate is not None and (gate.dtype != torch.bfloat16 or gate.stride(1) != 1)):
         raise KernelError("grouped product: weights (and the gate) are bfloat16")
     fn = _fn("grouped_gemm", "pbe_grouped_gemm",
              [c_void_p, c_int, c_int, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p, c_int, c_int, c_ll, c_int, c_int, c_int,
-              c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+              c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p])
     ldg = 0
     if gate is not None:
-        ldg = gate.stride(0) if T > 1 else max(gate.stride(0), groups)
+        ldg = gate.stride(0) if T > 1 else max(gate.stride(0), groups * (N if gate_each else 1))
     _check(fn(_ptr(a), _dtype_code(a), int(lda), int(a_group), _ptr(w), int(w_group), int(wk), int(wn), _ptr(out),
               _dtype_code(out), int(ldo), int(out_group), int(T), int(K), int(N), int(groups), _ptr(tiles),
               int(num_tiles), _ptr(gate), int(ldg), int(rot), int(rot_dims), _ptr(inv_freq), _ptr(positions),
-              _stream()), "grouped_gemm")
+              float(rot_scale), 1 if gate_each else 0, _stream()), "grouped_gemm")
     return out
 
 
 def grouped_heads(a: torch.Tensor, lda: int, head_stride: int, K: int, w: torch.Tensor, w_head_stride: int,
                   wk: int, wn: int, N: int, out: torch.Tensor, ldo: int, out_head_stride: int, T: int, H: int,
                   rot: int = 0, rot_dims: int = 0, inv_freq: Optional[torch.Tensor] = None,
-                  positions: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  positions: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                  rot_scale: float = 1.0, gate_each: bool = False) -> torch.Tensor:
     """``head_product`` on the tensor cores: the same arguments and result; ``a`` bfloat16 or float32
     (rounded to bfloat16 as an operand), ``w`` and ``gate`` bfloat16, float32 sums."""
     return _grouped(a, lda, head_stride, w, w_head_stride, wk, wn, out, ldo, out_head_stride, T, K, N, H, None, 0,
-                    gate, rot, rot_dims, inv_freq, positions)
+                    gate, rot, rot_dims, inv_freq, positions, rot_scale, gate_each)
 
 
 def run_tiles(counts: torch.Tensor, max_tiles: int):
@@ -1712,3 +1740,149 @@ def grouped_runs(a: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, out_dtyp
         raise KernelError("grouped_runs: the weights are [G, N, K]")
     out = torch.empty((rows, N), dtype=out_dtype, device=a.device)
     return _grouped(a, K, 0, w, N * K, 1, K, out, N, 0, rows, K, N, G, tiles, tiles.shape[0])
+
+
+# ------------------------------------------------------------------ norms with one learned number, mix over depth
+def unit_norm(x: torch.Tensor, y1: Optional[torch.Tensor], y2: Optional[torch.Tensor], alpha: float, gain: torch.Tensor,
+              eps: float, lp_dtype: Optional[torch.dtype] = None, normed: Optional[torch.Tensor] = None,
+              stack: Optional[torch.Tensor] = None, n_prev: int = 0, mix: Optional[torch.Tensor] = None,
+              mixed: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+              sum_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """n = g * v / sqrt(mean(v^2) + eps) with v = alpha * x + y1 + y2 (float32; ``gain`` holds the one
+    number g; y1, y2 optional, in one dtype).  ``normed`` (float32 [T, W]) receives n, ``sum_out``
+    (float32 [T, W]) receives v.  With ``mix`` (float32 [n_prev + 1]) and ``stack`` (float32
+    [>= n_prev, T, W], the earlier results), ``mixed`` receives sum_j mix[j] stack[j] + mix[n_prev] n.
+    Returns a copy of the last of these (the mix if there is one, else n) in ``lp_dtype``, or None
+    when ``lp_dtype`` is None.  With ``rows`` (int32 [n]) output row i is made from row rows[i]."""
+    _need_cuda(x, y1, y2, gain, normed, stack, mix, mixed, rows, sum_out)
+    _need_contiguous(x, y1, y2, normed, stack, mix, mixed, rows, sum_out)
+    if x.dtype != torch.float32 or x.dim() != 2 or gain.dtype != torch.float32 or gain.numel() != 1:
+        raise KernelError("unit_norm: x is float32 [T, W], the gain one float32 number")
+    T, d = x.shape
+    ys = [y for y in (y1, y2) if y is not None]
+    for y in ys:
+        if y.shape != x.shape or y.dtype != ys[0].dtype:
+            raise KernelError("unit_norm: the branch outputs have x's shape and one dtype")
+    if y1 is None and y2 is not None:
+        y1, y2 = y2, None
+    n = T if rows is None else rows.numel()
+    if rows is not None and (rows.dtype != torch.int32 or sum_out is not None):
+        raise KernelError("unit_norm: rows are int32, and gathered rows write no sum back")
+    for o in (normed, mixed):
+        if o is not None and (o.dtype != torch.float32 or tuple(o.shape) != (n, d)):
+            raise KernelError("unit_norm: float32 outputs are [rows, W]")
+    if sum_out is not None and (sum_out.dtype != torch.float32 or sum_out.shape != x.shape):
+        raise KernelError("unit_norm: the sum is float32 [T, W]")
+    stride = 0
+    if mix is not None:
+        if mix.dtype != torch.float32 or mix.numel() != n_prev + 1:
+            raise KernelError("unit_norm: the mix is float32 [n_prev + 1]")
+        if n_prev > 0:
+            if stack is None or stack.dtype != torch.float32 or stack.dim() != 3 or stack.shape[0] < n_prev or \
+                    tuple(stack.shape[1:]) != (T, d):
+                raise KernelError("unit_norm: the stack is float32 [>= n_prev, T, W]")
+            stride = stack.stride(0)
+    if d * 4 > 200 * 1024:
+        raise KernelError(f"unit_norm: a row of {d} floats does not fit in shared memory")
+    lp = torch.empty((n, d), dtype=lp_dtype, device=x.device) if lp_dtype is not None else None
+    fn = _fn("unit_norm", "pbe_unit_norm",
+             [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_ll, c_int,
+              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), _ptr(y1), _ptr(y2), _dtype_code(ys[0]) if ys else F32, float(alpha), _ptr(gain), float(eps),
+              _ptr(sum_out), _ptr(normed), _ptr(stack if mix is not None and n_prev > 0 else None), int(stride),
+              int(n_prev), _ptr(mix), _ptr(mixed), _ptr(lp), _dtype_code(lp) if lp is not None else F32, _ptr(rows), n, d,
+              _stream()), "unit_norm")
+    return lp
+
+
+def embedding_unit_norm(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, gain: torch.Tensor, eps: float,
+                        lp_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """out[t] = g * e / sqrt(mean(e^2) + eps), e = table[ids[t]], float32; also returned in ``lp_dtype``
+    (None: no copy)."""
+    _need_cuda(out, table, ids, gain)
+    _need_contiguous(out, table, ids)
+    T, d = out.shape
+    if out.dtype != torch.float32 or ids.dtype != torch.int32 or table.shape[1] != d or ids.numel() != T:
+        raise KernelError("embedding_unit_norm: float32 rows from int32 ids, widths agree")
+    if gain.dtype != torch.float32 or gain.numel() != 1:
+        raise KernelError("embedding_unit_norm: the gain is one float32 number")
+    lp = torch.empty((T, d), dtype=lp_dtype, device=out.device) if lp_dtype is not None else None
+    fn = _fn("unit_norm", "pbe_embedding_unit_norm",
+             [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(out), _ptr(lp), _dtype_code(lp) if lp is not None else F32, _ptr(table), _dtype_code(table), _ptr(ids),
+              _ptr(gain), T, d, table.shape[0], float(eps), _stream()), "embedding_unit_norm")
+    return lp
+
+
+# ------------------------------------------------------------------ gated diagonal linear recurrence
+def recurrence_gates(u: torch.Tensor, w_r: torch.Tensor, w_i: torch.Tensor, b_r: torch.Tensor, b_i: torch.Tensor,
+                     lam: torch.Tensor, rate: float):
+    """(a, b), float32 [T, C]: with r = sigmoid(R u + b_r) and i = sigmoid(I u + b_i), R and I block
+    diagonal (``w_r``, ``w_i`` [B, C/B, C/B], [out, in]), a = exp(-rate * r * softplus(lam)) and
+    b = sqrt(1 - a^2) * i * u; all float32 arithmetic.  ``u`` [T, C] may be a column slice."""
+    _need_cuda(u, w_r, w_i, b_r, b_i, lam)
+    _need_contiguous(w_r, w_i, b_r, b_i, lam)
+    _column_slice(u, "recurrence_gates")
+    T, C = u.shape
+    B, n = w_r.shape[0], w_r.shape[1]
+    if tuple(w_r.shape) != (B, n, n) or w_i.shape != w_r.shape or B * n != C or w_i.dtype != w_r.dtype:
+        raise KernelError("recurrence_gates: the gate maps are [B, C/B, C/B] in one dtype")
+    for v in (b_r, b_i, lam):
+        if v.dtype != torch.float32 or v.numel() != C:
+            raise KernelError("recurrence_gates: gate biases and lam are float32 [C]")
+    a = torch.empty((T, C), dtype=torch.float32, device=u.device)
+    b = torch.empty((T, C), dtype=torch.float32, device=u.device)
+    ld = u.stride(0) if T > 1 else max(u.stride(0), C)
+    fn = _fn("gated_recurrence", "pbe_recurrence_gates",
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(u), ld, _dtype_code(u), _ptr(w_r), _ptr(w_i), _dtype_code(w_r), _ptr(b_r), _ptr(b_i), _ptr(lam),
+              float(rate), _ptr(a), _ptr(b), T, C, B, _stream()), "recurrence_gates")
+    return a, b
+
+
+SCAN_ACTIVATIONS = {None: 0, "gelu_tanh": 1}
+
+
+def gated_scan(a: torch.Tensor, b: torch.Tensor, y: Optional[torch.Tensor], state: torch.Tensor, q_start: torch.Tensor,
+               q_len: torch.Tensor, slots: torch.Tensor, num_requests: int, out_dtype: torch.dtype,
+               activation: Optional[str] = "gelu_tanh", plan=None, zero_out: bool = False) -> torch.Tensor:
+    """S_t = a_t S_(t-1) + b_t per channel over each request's rows, from and to the request's row of
+    ``state`` (float32 [slots, C]); returns S_t * act(y_t) as [T, C] in ``out_dtype`` (``y`` [T, C],
+    possibly a column slice, or None: S itself).  ``plan`` (a ``RecurrencePlan`` with chunks): long
+    portions run as chunks side by side, in three launches."""
+    _need_cuda(a, b, y, state, q_start, q_len, slots)
+    _need_contiguous(a, b, state)
+    T, C = a.shape
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or b.shape != a.shape:
+        raise KernelError("gated_scan: a and b are float32 [T, C]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != C:
+        raise KernelError("gated_scan: the state is float32 [slots, C]")
+    if activation not in SCAN_ACTIVATIONS:
+        raise KernelError(f"gated_scan: unknown activation {activation!r}")
+    ldy = 0
+    if y is not None:
+        _column_slice(y, "gated_scan")
+        if y.shape != a.shape or y.dtype != out_dtype:
+            raise KernelError("gated_scan: y is [T, C] in the output's dtype")
+        ldy = y.stride(0) if T > 1 else max(y.stride(0), C)
+    out = (torch.zeros if zero_out else torch.empty)((T, C), dtype=out_dtype, device=a.device)
+    fn = _fn("gated_recurrence", "pbe_gated_scan",
+             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    code, act = _dtype_code(out), SCAN_ACTIVATIONS[activation]
+    if plan is None or plan.num_chunks == 0:
+        _check(fn(_ptr(a), _ptr(b), _ptr(y), ldy, _ptr(out), code, _ptr(state), None, None, None, int(num_requests),
+                  _ptr(q_start), _ptr(q_len), _ptr(slots), C, act, 0, _stream()), "gated_scan")
+        return out
+    scratch_s = torch.empty((plan.num_chunks, C), dtype=torch.float32, device=a.device)
+    scratch_p = torch.empty((plan.num_chunks, C), dtype=torch.float32, device=a.device)
+    if plan.num_first_pass:
+        _check(fn(_ptr(a), _ptr(b), None, 0, None, code, _ptr(state), _ptr(scratch_s), _ptr(scratch_p),
+                  _ptr(plan.first_pass), plan.num_first_pass, None, None, None, C, act, 1, _stream()), "gated_scan")
+    sfn = _fn("gated_recurrence", "pbe_chunk_starts", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(sfn(_ptr(plan.scan), plan.num_scan, _ptr(state), _ptr(scratch_s), _ptr(scratch_p), C, _stream()),
+           "chunk_starts")
+    _check(fn(_ptr(a), _ptr(b), _ptr(y), ldy, _ptr(out), code, _ptr(state), _ptr(scratch_s), _ptr(scratch_p),
+              _ptr(plan.second_pass), plan.num_second_pass, None, None, None, C, act, 2, _stream()), "gated_scan")
+    return out

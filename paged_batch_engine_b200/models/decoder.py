@@ -25,6 +25,17 @@ class DecoderModel:
         self.blocks = [build_block(b, dtype, self.device) for b in spec.blocks]
         self._native = None       # the blocks' descriptors for the host library (False: not this model)
         self.final_norm = build_part("norm", spec.final_norm, dtype, self.device)
+        self.embedding_norm = None
+        if spec.embedding_norm is not None:
+            self.embedding_norm = build_part("norm", spec.embedding_norm, dtype, self.device)
+            if not hasattr(self.embedding_norm, "embed"):
+                raise TypeError("the embedding's norm must be able to norm gathered rows (ScalarRMSNorm)")
+        if spec.depth_stack not in (None, "mix", "plain"):
+            raise ValueError(f"unknown depth_stack {spec.depth_stack!r}")
+        if spec.depth_stack is not None and (spec.residual_streams != 1 or spec.embedding_scale != 1.0
+                                             or spec.position_table_name is not None
+                                             or any(st.input_mix for st in spec.run_order)):
+            raise ValueError("a depth stack goes with one residual stream, an unscaled embedding and no input mixes")
         self.embed = None
         self.lm_head = None
         self.position_table = None
@@ -44,6 +55,8 @@ class DecoderModel:
             specs.append(ParamSpec(s.position_table_name, (s.max_position, s.hidden_size)))
         for name in dict.fromkeys(st.input_mix for st in s.run_order if st.input_mix is not None):
             specs.append(ParamSpec(name, (s.hidden_size, 2 * s.hidden_size)))
+        if self.embedding_norm is not None:
+            specs += self.embedding_norm.param_specs(s.embedding_norm_name)
         for b in self.blocks:
             specs += b.param_specs()
         specs += self.final_norm.param_specs(s.final_norm_name)
@@ -61,6 +74,8 @@ class DecoderModel:
             self.position_table = tensors.pop(s.position_table_name).to(self.embed.dtype).contiguous()
         for name in dict.fromkeys(st.input_mix for st in s.run_order if st.input_mix is not None):
             self.input_mixes[name] = tensors.pop(name).contiguous()
+        if self.embedding_norm is not None:
+            self.embedding_norm.load(tensors, s.embedding_norm_name)
         for b in self.blocks:
             b.load(tensors)
         self.final_norm.load(tensors, s.final_norm_name)
@@ -74,6 +89,9 @@ class DecoderModel:
         jobs = [("elementwise", None)] + ops.gemm_libraries(self.dtype)
         for b in self.blocks:
             jobs += b.kernel_libraries(self.dtype)
+        for norm in (self.embedding_norm, self.final_norm):
+            if norm is not None:
+                jobs += norm.kernel_libraries(self.dtype)
         seen, out = set(), []
         for name, defines in jobs:
             key = (name, tuple(sorted((defines or {}).items())))
@@ -119,6 +137,7 @@ class DecoderModel:
             ok = all(d is not None for d in descs) and all(st.writes_cache and st.input_mix is None
                                                            for st in self.spec.run_order)
             ok = ok and self.spec.embedding_scale == 1.0 and self.spec.position_table_name is None
+            ok = ok and self.spec.embedding_norm is None and self.spec.depth_stack is None
             self._native = descs if ok else False
         return self._native or None
 
@@ -162,8 +181,18 @@ class DecoderModel:
         wanted rows, [wanted, vocab]."""
         s = self.spec
         T = ctx.num_tokens
-        residual = torch.empty((T, s.hidden_size), dtype=torch.float32, device=self.device)
-        if s.embedding_scale != 1.0 or self.position_table is not None:
+        stack = None
+        if s.depth_stack is not None:
+            from ..parts.block import DepthStack
+            stack = DepthStack(len(s.run_order), T, s.hidden_size, self.dtype, self.device, s.depth_stack == "mix")
+            residual = stack.first()
+        else:
+            residual = torch.empty((T, s.hidden_size), dtype=torch.float32, device=self.device)
+        first_lp = None
+        if self.embedding_norm is not None:
+            first_lp = self.embedding_norm.embed(residual, self.embed, ctx.token_ids,
+                                                 stack.lp_dtype() if stack is not None else None)
+        elif s.embedding_scale != 1.0 or self.position_table is not None:
             # a learned position row follows the token's place in the sequence
             ops.embedding_positions(residual, self.embed, ctx.token_ids, s.embedding_scale, self.position_table,
                                     ctx.positions)
@@ -177,6 +206,11 @@ class DecoderModel:
         if s.residual_streams > 1:
             # several residual streams, [T, S, W]: every one starts as the embedding
             residual = residual.unsqueeze(1).expand(T, s.residual_streams, s.hidden_size).contiguous()
+        if stack is not None:
+            if first_lp is None and stack.lp_dtype() is not None:
+                first_lp = residual.to(stack.lp_dtype())
+            stack.start(first_lp)
+            residual = stack
         delta = None
         native = self._native_descs(ctx)
         if native is not None:
@@ -196,6 +230,8 @@ class DecoderModel:
                     residual, delta = block.forward(residual, delta, ctx, cache)
         if ctx.num_wanted == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)
+        if stack is not None:
+            residual = stack.current
         h = self.final_norm.add_norm(residual, delta, rows=ctx.want_rows)
         logits = ops.linear(h, self.lm_head, None, out_dtype=torch.float32)
         if s.logit_scale != 1.0 or s.logit_softcap:

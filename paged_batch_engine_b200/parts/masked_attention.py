@@ -25,8 +25,10 @@ def log_bucket(distance: int, rows: int, far: float) -> int:
 
 class MaskedAttention(Mixer):
     """q, k, v (and the gate) = x W^T as one fused product; an RMS norm over each query and key
-    head with one gain vector per projection, shared by the heads (``qk_norm``); no rotation;
-    score = q . k * ``scale`` (+ a learned bias by head and distance bucket, ``distance_bias``);
+    head with one gain vector per projection, shared by the heads (``qk_norm``; "unit": the heads
+    are divided by their root mean square and there are no gain tensors); no rotation;
+    score = q . k * ``scale`` (times a learned number per query head, ``head_temperature``: tensor
+    ``temp`` [H]) (+ a learned bias by head and distance bucket, ``distance_bias``);
     softmax over the keys the mask lets the row see; output projection.
 
     Options, all constants of the part:
@@ -38,7 +40,7 @@ class MaskedAttention(Mixer):
     tensor's own first size (``rows`` only says how many to make when weights are drawn at random).
     ``unit_sink``: the softmax's denominator has one more term e^0 that carries no value.
     ``out_gate``: the concatenated heads are multiplied by sigmoid(W_g x) element by element.
-    ``proj_bias``: q, k, v and the output projection have biases (``<name>.b``).
+    ``proj_bias``: q, k, v and the output projection have biases (``<name>.b``); "qkv": only q, k and v.
     Keys are ``key_dim`` wide and values ``value_dim``.
 
     What a row can see always lies within the last ``mask_size`` positions, so the pages behind
@@ -48,14 +50,14 @@ class MaskedAttention(Mixer):
     [hidden, H*E], q.norm / k.norm [D], rel [B, H], g [H*E, hidden], and ``.b`` beside q, k, v, o
     (``tensor_names`` renames them)."""
     TENSOR_NAMES = dict(q="q", k="k", v="v", o="o", q_norm="q.norm", k_norm="k.norm", rel="rel", g="g",
-                        bias_suffix=".b")
+                        temp="temp", bias_suffix=".b")
     decode_capturable = True      # stepped from the step's device arrays alone
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
                  scale: float, eps: float, dtype, device, mask: Optional[str] = None,
                  mask_size: Optional[int] = None, qk_norm: bool = True, distance_bias: Optional[dict] = None,
-                 unit_sink: bool = False, out_gate: bool = False, proj_bias: bool = False,
-                 tensor_names: Optional[dict] = None):
+                 unit_sink: bool = False, out_gate: bool = False, proj_bias=False,
+                 head_temperature: bool = False, tensor_names: Optional[dict] = None):
         unknown = set(tensor_names or {}) - set(self.TENSOR_NAMES)
         if unknown:
             raise ValueError(f"tensor_names knows {sorted(self.TENSOR_NAMES)}; got {sorted(unknown)}")
@@ -72,8 +74,12 @@ class MaskedAttention(Mixer):
         self.key_dim, self.value_dim = key_dim, value_dim
         self.scale, self.eps = float(scale), float(eps)
         self.mask, self.mask_size = mask, (int(mask_size) if mask is not None else None)
-        self.qk_norm, self.unit_sink, self.out_gate = bool(qk_norm), bool(unit_sink), bool(out_gate)
-        self.proj_bias = bool(proj_bias)
+        if qk_norm not in (True, False, "unit") or proj_bias not in (True, False, "qkv"):
+            raise ValueError('qk_norm is True, False or "unit"; proj_bias True, False or "qkv"')
+        self.qk_norm, self.unit_sink, self.out_gate = qk_norm, bool(unit_sink), bool(out_gate)
+        self.proj_bias, self.head_temperature = proj_bias, bool(head_temperature)
+        if self.head_temperature and not qk_norm:
+            raise ValueError("a temperature per head rides on the head norm")
         self.bias_rows = self.bias_far = None
         if distance_bias is not None:
             self.bias_rows, self.bias_far = int(distance_bias.get("rows") or 16), float(distance_bias["far"])
@@ -82,6 +88,7 @@ class MaskedAttention(Mixer):
         self.dtype, self.device = dtype, device
         self.tile_rows = ops.masked_tile_rows(dtype, key_dim, value_dim)
         self.w_in = self.b_in = self.w_o = self.b_o = self.q_gain = self.k_gain = self.bias_by_distance = None
+        self.q_head_scale = None
 
     # ---- what it keeps
     def cache_need(self):
@@ -109,9 +116,13 @@ class MaskedAttention(Mixer):
                  ParamSpec(prefix + n["v"], (G * E, w)), ParamSpec(prefix + n["o"], (w, H * E))]
         if self.proj_bias:
             specs += [ParamSpec(prefix + n["q"] + b, (H * D,)), ParamSpec(prefix + n["k"] + b, (G * D,)),
-                      ParamSpec(prefix + n["v"] + b, (G * E,)), ParamSpec(prefix + n["o"] + b, (w,))]
-        if self.qk_norm:
+                      ParamSpec(prefix + n["v"] + b, (G * E,))]
+            if self.proj_bias is True:
+                specs.append(ParamSpec(prefix + n["o"] + b, (w,)))
+        if self.qk_norm is True:
             specs += [ParamSpec(prefix + n["q_norm"], (D,)), ParamSpec(prefix + n["k_norm"], (D,))]
+        if self.head_temperature:
+            specs.append(ParamSpec(prefix + n["temp"], (H,)))
         if self.bias_rows:
             specs.append(ParamSpec(prefix + n["rel"], (self.bias_rows, H), free_dims=(0,)))
         if self.out_gate:
@@ -132,10 +143,15 @@ class MaskedAttention(Mixer):
         self.w_o = tensors.pop(prefix + n["o"]).contiguous()
         if self.proj_bias:
             self.b_in = torch.cat([tensors.pop(prefix + n[x] + b).to(torch.float32) for x in "qkv"]).contiguous()
-            self.b_o = tensors.pop(prefix + n["o"] + b).to(torch.float32).contiguous()
-        if self.qk_norm:
+            if self.proj_bias is True:
+                self.b_o = tensors.pop(prefix + n["o"] + b).to(torch.float32).contiguous()
+        if self.qk_norm is True:
             self.q_gain = tensors.pop(prefix + n["q_norm"]).to(torch.float32).contiguous()
             self.k_gain = tensors.pop(prefix + n["k_norm"]).to(torch.float32).contiguous()
+        elif self.qk_norm == "unit":
+            self.q_gain = self.k_gain = torch.ones(self.key_dim, dtype=torch.float32, device=self.w_in.device)
+        if self.head_temperature:
+            self.q_head_scale = tensors.pop(prefix + n["temp"]).to(torch.float32).contiguous()
         if self.bias_rows:
             rel = tensors.pop(prefix + n["rel"]).to(torch.float32)
             self.bias_rows = int(rel.shape[0])
@@ -155,7 +171,8 @@ class MaskedAttention(Mixer):
         writes = cache.writes
         q = ops.head_norm_write(proj, q_off, k_off, v_off, self.b_in, self.q_gain, self.k_gain,
                                 group.slots if writes else None, cache.k if writes else None,
-                                cache.v if writes else None, H, G, D, E, ctx.page_tokens, self.eps)
+                                cache.v if writes else None, H, G, D, E, ctx.page_tokens, self.eps,
+                                q_head_scale=self.q_head_scale)
         meta = ctx.attention_work(cache.group, H // G, self.tile_rows, self.mask_size, H, E)
         gate = proj[:, g_off:] if self.out_gate else None
         out = ops.masked_attention(q, cache.k, cache.v, meta, H, G, self.scale, self.mask, self.mask_size,

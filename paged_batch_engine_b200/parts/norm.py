@@ -51,6 +51,50 @@ class RMSNorm(Norm):
                                  delta_scale=scale)
 
 
+class ScalarRMSNorm(Norm):
+    """y = g * x / sqrt(mean(x^2) + eps) with ONE learned number g for all coordinates (the checkpoint
+    tensor has no axes), all in float32.  As a norm after a plain residual add it behaves like
+    ``RMSNorm`` (residual += delta, then the norm); layers that normalise after the sum call
+    ``norm_sum`` instead."""
+
+    def __init__(self, size: int, eps: float, dtype, device, weight_name: str = "weight"):
+        self.size, self.eps, self.dtype, self.device = int(size), float(eps), dtype, device
+        self.weight_name = weight_name
+        self.gain = None
+
+    def param_specs(self, prefix):
+        return [ParamSpec(prefix + self.weight_name, ())]
+
+    def load(self, tensors, prefix):
+        self.gain = tensors[prefix + self.weight_name].to(torch.float32).reshape(1).contiguous()
+
+    def kernel_libraries(self, dtype):
+        return [("unit_norm", None)]
+
+    def add_norm(self, residual, delta, rows=None, out_dtype=None):
+        if isinstance(delta, DeltaSum):
+            if delta.scale != 1.0:
+                raise ValueError("a norm with one gain adds unscaled branches")
+            a, b = delta.a, delta.b
+        else:
+            a, b = delta, None
+        write_back = rows is None and (a is not None or b is not None)
+        return ops.unit_norm(residual, a, b, 1.0, self.gain, self.eps, out_dtype or self.dtype, rows=rows,
+                             sum_out=residual if write_back else None)
+
+    def norm_sum(self, x, y, alpha, lp_dtype, normed=None, stack=None, n_prev=0, mix=None, mixed=None):
+        """g * n(alpha * x + y) (``y`` a tensor, a ``DeltaSum`` of two, or None): float32 into ``normed``;
+        with ``mix`` the learned mix over ``stack[:n_prev]`` and this result into ``mixed``; the last of
+        these also returned in ``lp_dtype`` (None: not)."""
+        a, b = (y.a, y.b) if isinstance(y, DeltaSum) else (y, None)
+        return ops.unit_norm(x, a, b, alpha, self.gain, self.eps, lp_dtype, normed=normed, stack=stack, n_prev=n_prev,
+                             mix=mix, mixed=mixed)
+
+    def embed(self, out, table, ids, lp_dtype):
+        """The norm of gathered embedding rows, float32 into ``out``; a copy in ``lp_dtype`` returned."""
+        return ops.embedding_unit_norm(out, table, ids, self.gain, self.eps, lp_dtype)
+
+
 class LayerNorm(Norm):
     """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w + b on x = residual + delta, all
     in float32 (the variance from the deviations, in a second pass over the row).
@@ -133,3 +177,4 @@ class PendingUpdate:
 
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
 register_part("norm", "layernorm", LayerNorm, replace=True)
+register_part("norm", "scalar_rmsnorm", ScalarRMSNorm, replace=True)

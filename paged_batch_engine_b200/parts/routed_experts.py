@@ -8,6 +8,7 @@ import torch
 from ..csrc import ops
 from ..weights.loader import ParamSpec
 from .base import FeedForward, register_part
+from .mlp import SwiGLU
 
 
 class RoutedExperts(FeedForward):
@@ -18,6 +19,11 @@ class RoutedExperts(FeedForward):
     only experts of the ``keep`` best groups can be chosen (``groups`` 1: all can); the ``top``
     allowed experts with the largest scores are chosen; g = s / (sum of the chosen s + 1e-20) *
     ``scale`` (with one group and scale 1 that is the softmax over the chosen logits alone).
+    ``router_score`` "sigmoid": s = sigmoid(z) per expert instead of the softmax.  ``correction``: a
+    learned vector (tensor ``correction`` [E]) added to s for the choice only (groups and experts are
+    ranked by s + correction; the weights use s).  ``group_rank`` "top2_sum": a group's score is the
+    sum of its two largest choice scores.  ``shared_size`` F_s: one more expert of that width (tensors
+    ``shared.gate``, ``shared.up``, ``shared.down``) runs for every token and is added, unweighted.
     Experts have no biases.  ``activation``: "silu" as above, or "capped_swish" with ``limit`` L and
     ``alpha`` a: g <- min(W_gate x, L), u <- clamp(W_up x, -L, L), hidden = g sigmoid(a g) (u + 1).
 
@@ -35,7 +41,8 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, dtype, device,
                  groups: int = 1, keep: Optional[int] = None, scale: float = 1.0, many_rows: int = 64,
                  router_name: str = "router", expert_prefix: str = "e", activation: str = "silu",
-                 limit: float = 0.0, alpha: float = 1.0):
+                 limit: float = 0.0, alpha: float = 1.0, router_score: str = "softmax", correction: bool = False,
+                 group_rank: str = "max", shared_size: Optional[int] = None, shared_prefix: str = "shared."):
         keep = groups if keep is None else keep
         if num_experts % groups or not 1 <= keep <= groups or not 1 <= top <= keep * (num_experts // groups):
             raise ValueError("experts divide into equal groups, 1 <= keep <= groups, and the kept groups hold "
@@ -51,16 +58,30 @@ class RoutedExperts(FeedForward):
         if activation == "capped_swish" and not limit > 0:
             raise ValueError("the capped activation needs a positive limit")
         self.activation, self.limit, self.alpha = activation, float(limit), float(alpha)
+        if router_score not in ops.ROUTER_SCORES or group_rank not in ops.GROUP_RANKS:
+            raise ValueError(f"router scores: {sorted(ops.ROUTER_SCORES)}; group ranks: {sorted(ops.GROUP_RANKS)}")
+        self.router_score, self.group_rank, self.has_correction = router_score, group_rank, bool(correction)
         self.dtype, self.device = dtype, device
-        self.w_router = self.w_gate_up = self.w_down = None
+        self.w_router = self.w_gate_up = self.w_down = self.correction = None
+        self.shared, self.shared_prefix = None, shared_prefix
+        if shared_size:
+            if activation != "silu":
+                raise ValueError("the shared expert is silu-gated")
+            self.shared = SwiGLU(hidden_size, int(shared_size), dtype, device,
+                                 tensor_names=dict(gate="gate", up="up", down="down"), weight_suffix="")
 
     def kernel_libraries(self, dtype):
         tiled = [("grouped_gemm", None)] if dtype == torch.bfloat16 else []
-        return [("routed_experts", None), ("elementwise", None)] + tiled + ops.gemm_libraries(dtype)
+        shared = self.shared.kernel_libraries(dtype) if self.shared is not None else []
+        return [("routed_experts", None), ("elementwise", None)] + tiled + ops.gemm_libraries(dtype) + shared
 
     def param_specs(self, prefix):
         i, h = self.intermediate_size, self.hidden_size
         specs = [ParamSpec(prefix + self.router_name, (self.num_experts, h))]
+        if self.has_correction:
+            specs.append(ParamSpec(prefix + "correction", (self.num_experts,)))
+        if self.shared is not None:
+            specs += self.shared.param_specs(prefix + self.shared_prefix)
         for e in range(self.num_experts):
             p = f"{prefix}{self.expert_prefix}{e}."
             specs += [ParamSpec(p + "gate", (i, h)), ParamSpec(p + "up", (i, h)), ParamSpec(p + "down", (h, i))]
@@ -68,6 +89,10 @@ class RoutedExperts(FeedForward):
 
     def load(self, tensors, prefix):
         self.w_router = tensors.pop(prefix + self.router_name).contiguous()
+        if self.has_correction:
+            self.correction = tensors.pop(prefix + "correction").to(torch.float32).contiguous()
+        if self.shared is not None:
+            self.shared.load(tensors, prefix + self.shared_prefix)
         names = [f"{prefix}{self.expert_prefix}{e}." for e in range(self.num_experts)]
         # an expert's gate rows followed by its up rows: one product gives both
         self.w_gate_up = torch.stack([torch.cat([tensors.pop(p + "gate"), tensors.pop(p + "up")], dim=0)
@@ -77,20 +102,23 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         T = x.shape[0]
         logits = ops.linear(x, self.w_router, None, out_dtype=torch.float32)
-        chosen, weights = ops.route(logits, self.top, self.groups, self.keep, self.scale)
+        chosen, weights = ops.route(logits, self.top, self.groups, self.keep, self.scale, self.router_score,
+                                    self.correction, self.group_rank)
+        # the shared expert's output rides into the launch that adds a token's experts up
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
         if x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16:
             if T < min(self.many_rows, self.MANY_ROWS_TILED):
-                return self._rows(x, chosen, weights)
-            return self._tiled(x, chosen, weights)
+                return self._rows(x, chosen, weights, shared)
+            return self._tiled(x, chosen, weights, shared)
         if T < self.many_rows or getattr(ctx, "captured", False):
-            return self._rows(x, chosen, weights)
-        return self._sorted(x, chosen, weights)
+            return self._rows(x, chosen, weights, shared)
+        return self._sorted(x, chosen, weights, shared)
 
-    def _rows(self, x, chosen, weights):
+    def _rows(self, x, chosen, weights, shared=None):
         return ops.expert_rows(x, self.w_gate_up, self.w_down, chosen, weights, self.activation, self.limit,
-                               self.alpha)
+                               self.alpha, addend=shared)
 
-    def _tiled(self, x, chosen, weights):
+    def _tiled(self, x, chosen, weights, shared=None):
         """bfloat16: rows sorted by expert, every expert's run padded to whole row tiles, and one
         launch per projection that multiplies every tile with its expert's matrix on the tensor
         cores.  Nothing is read on the host."""
@@ -103,9 +131,9 @@ class RoutedExperts(FeedForward):
         hidden = torch.empty((rows.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
         ops.gated_activation(gu, hidden, self.activation, self.limit, self.alpha)
         out = ops.grouped_runs(hidden, self.w_down, tiles, self.dtype)
-        return ops.expert_scatter(out, chosen, place, start, weights, T)
+        return ops.expert_scatter(out, chosen, place, start, weights, T, addend=shared)
 
-    def _sorted(self, x, chosen, weights):
+    def _sorted(self, x, chosen, weights, shared=None):
         """Rows sorted by expert, one product per expert and projection over its run of rows."""
         T = x.shape[0]
         counts, place = ops.expert_places(chosen, self.num_experts)
@@ -122,7 +150,7 @@ class RoutedExperts(FeedForward):
                 ops.gated_activation(gu, hidden[lo:hi], self.activation, self.limit, self.alpha)
                 out[lo:hi] = ops.linear(hidden[lo:hi], self.w_down[e], None, out_dtype=self.dtype)
             lo = hi
-        return ops.expert_scatter(out, chosen, place, start, weights, T)
+        return ops.expert_scatter(out, chosen, place, start, weights, T, addend=shared)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
