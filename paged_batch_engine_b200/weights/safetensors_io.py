@@ -106,7 +106,8 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Dict[str, s
         f.write(blob)
         for name in order:
             t = tensors[name].detach().contiguous().cpu()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            # a tensor without axes (one number) is stored as its one element
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
 
 
 def open_model_files(folder: str) -> List[SafetensorsFile]:

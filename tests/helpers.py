@@ -344,3 +344,115 @@ def make_gusorax_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str
         w[k] = t.to(w[k].dtype)
     save_file(w, f)
     return str(path)
+
+
+# ---------------------------------------------------------------- Mobunex: tiny configurations
+def _mwin(heads, kv, dim, vdim, size, scale):
+    return dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=scale, mask=dict(size=size))
+
+
+def _mlat(heads, dim, rot_dim, rot_dims, vdim, kv_rank, q_rank, base, scale, size, scaling=None):
+    rot = dict(base=base, dims=rot_dims)
+    if scaling:
+        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, scale=scale,
+                mask=dict(size=size), rot=rot)
+
+
+def _mrec(width, blocks, conv):
+    return dict(width=width, blocks=blocks, conv=conv)
+
+
+def _mmoe(ff, experts, top, count, keep, shared=None):
+    d = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top, groups=dict(count=count, keep=keep)))
+    if shared:
+        d["shared"] = dict(ff=shared)
+    return d
+
+
+# four query heads on two key heads with values wider than keys and a window off the page grid; three
+# gate blocks and four taps; three groups of two experts of which two are kept, with a shared expert; a
+# latent layer without feed-forward whose slow pairs are stretched eightfold; one gate block, two taps
+MOB_A = dict(
+    architecture="Mobunex", width=64, vocab=300, norm=dict(eps=1e-5), postln_alpha=1.5,
+    layers=[
+        dict(type="attention", mixer=_mwin(4, 2, 16, 24, 21, 0.3), mlp=dict(kind="dense", ff=96)),
+        dict(type="rglru", mixer=_mrec(48, 3, 4), mlp=_mmoe(40, 6, 2, 3, 2, shared=24)),
+        dict(type="latent_attention", mixer=_mlat(3, 16, 8, 8, 24, 40, 24, 10000.0, 0.25, 40, (8.0, 64, 16.0, 2.0)),
+             mlp=None),
+        dict(type="rglru", mixer=_mrec(80, 1, 2), mlp=dict(kind="dense", ff=72)),
+    ])
+# alpha 1; a recurrent layer first, with a single tap (no convolution state) and no feed-forward; twenty
+# latent heads, only half of whose rotated part turns, no frequency scaling, a window of four whole
+# pages; five groups of two experts, no shared expert; as many key heads as query heads and a window
+# longer than any request
+MOB_B = dict(
+    architecture="Mobunex", width=96, vocab=211, norm=dict(eps=1e-6), postln_alpha=1.0,
+    layers=[
+        dict(type="rglru", mixer=_mrec(96, 6, 1), mlp=None),
+        dict(type="latent_attention", mixer=_mlat(20, 8, 4, 2, 8, 20, 16, 500.0, 0.3, 64), mlp=_mmoe(40, 10, 3, 5, 2)),
+        dict(type="attention", mixer=_mwin(6, 6, 32, 16, 600, 0.2), mlp=dict(kind="dense", ff=64)),
+    ])
+# eight query heads on one key head, heads of 64 (the tensor-core path in bfloat16), a window of 17;
+# groups of ONE expert and one expert chosen; a value wider than the latent; nine experts in three
+# groups, four chosen from two; five layers, so the depth mix reaches six terms
+MOB_C = dict(
+    architecture="Mobunex", width=128, vocab=257, norm=dict(eps=1e-6), postln_alpha=3.0,
+    layers=[
+        dict(type="attention", mixer=_mwin(8, 1, 64, 64, 17, 0.11), mlp=_mmoe(24, 8, 1, 8, 3, shared=48)),
+        dict(type="latent_attention", mixer=_mlat(8, 32, 16, 16, 56, 48, 40, 100000.0, 0.15, 33, (2.5, 32, 16.0, 2.0)),
+             mlp=_mmoe(32, 9, 4, 3, 2, shared=16)),
+        dict(type="rglru", mixer=_mrec(144, 4, 3), mlp=dict(kind="dense", ff=72)),
+        dict(type="attention", mixer=_mwin(2, 2, 24, 40, 1, 0.5), mlp=None),
+        dict(type="rglru", mixer=_mrec(40, 5, 2), mlp=None),
+    ])
+MOBUNEX = {"A": (MOB_A, 51, 8), "B": (MOB_B, 52, 16), "C": (MOB_C, 53, 8)}     # config, seed, page tokens
+
+
+def make_mobunex_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str:
+    """A model folder with seeded random weights through the engine's random-weights mode, then
+    reshaped so that no mechanism is a near-identity: projections large enough that every sublayer
+    matters beside the skip path, sharp softmaxes, temperatures, gate biases and decay rates spread
+    over a range, routers that decide and corrections that change the choice, depth mixes far from
+    "the last result only"."""
+    from paged_batch_engine_b200.config import load_config
+    from paged_batch_engine_b200.engine.runner import build_model
+    from paged_batch_engine_b200.weights import write_random_model
+    from safetensors.torch import load_file, save_file
+    _, typed = load_config(cfg)
+    model = build_model(typed, torch.float32, "cpu")
+    write_random_model(str(path), typed, model.param_specs(), seed, dtype)
+    f = os.path.join(str(path), "model.safetensors")
+    w = load_file(f)
+    g = torch.Generator().manual_seed(seed)
+    for k in list(w):
+        t = w[k].float()
+        leaf = k.split(".mix.")[-1] if ".mix." in k else k.split(".")[-1]
+        if k.endswith(".b"):
+            t = torch.randn(t.shape, generator=g) * 0.5
+        elif leaf in ("q", "k", "dq", "dkv", "uq", "uk", "x", "y") and t.dim() == 2:
+            t = t * 6.0
+        elif leaf in ("v", "o", "g", "uv") and t.dim() == 2:
+            t = t * 6.0
+        elif leaf in ("ra", "ri"):
+            t = t * 12.0
+        elif leaf == "temp":
+            t = 0.5 + 1.5 * torch.rand(t.shape, generator=g)
+        elif leaf == "lam":
+            t = torch.randn(t.shape, generator=g) * 1.5 - 1.0
+        elif leaf == "conv":
+            t = torch.randn(t.shape, generator=g) * 0.6
+        elif leaf in ("up", "down", "gate") and t.dim() == 2:
+            t = t * 4.5
+        elif leaf == "router":
+            t = t * 12.0
+        elif leaf == "correction":
+            t = torch.randn(t.shape, generator=g) * 0.3
+        elif leaf == "dwa":
+            t = torch.randn(t.shape, generator=g) * 0.6
+            t[-1] = 1.0
+        elif k == "head":
+            t = t * 8.0
+        w[k] = t.to(w[k].dtype)
+    save_file(w, f)
+    return str(path)
