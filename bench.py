@@ -218,9 +218,10 @@ def main():
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    ap.add_argument("--design", default=None, choices=["gebadra", "bavetar", "gusorax"],
+    ap.add_argument("--design", default=None, choices=["gebadra", "bavetar", "gusorax", "mobunex"],
                     help="instead of the default workload: prefill and decode of a few layers of this design at "
-                         "real layer sizes beside the Qwen2 model of equal sizes, with per-kernel rooflines")
+                         "real layer sizes beside the Qwen2 model of equal sizes (mobunex: beside Bavetar, the closest "
+                         "model of the engine), with per-kernel rooflines")
     ap.add_argument("--sizes", default="2048,4096", help="model widths of the --design comparison")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-extended", action="store_true",

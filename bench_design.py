@@ -1,12 +1,13 @@
 #!/usr/bin/env python3
 """A design beside the engine's closest existing model at equal layer sizes (random weights).
 
-    python bench.py --design gebadra|bavetar|gusorax [--steps K] [--warmup W] [--sizes 2048,4096]
+    python bench.py --design gebadra|bavetar|gusorax|mobunex [--steps K] [--warmup W] [--sizes 2048,4096]
 
 For each size: prefill (one 2,048-token prompt in one step) and decode (batch 8 from 2,048-token
 contexts, the captured decode step) throughput of a few layers of the design and of a Qwen2 model
 with the same width, heads, key/value heads, feed-forward width, vocabulary and number of
-layers; and the device time of the design's own kernels in one prompt step and one decode step,
+layers (Mobunex stands beside Bavetar, the engine's closest model: latent attention, a recurrent
+layer behind a short convolution, routed experts); and the device time of the design's own kernels in one prompt step and one decode step,
 each beside the like kernel of the Qwen2 model, with the fraction of its roofline (the slower of
 algorithmic bytes over the measured copy bandwidth and algorithmic FLOPs over the measured bf16
 GEMM rate).  Times are CUDA events on the launching stream after warm-up; the per-kernel times
@@ -70,6 +71,26 @@ def gusorax_config(width: int) -> dict:
     return dict(architecture="Gusorax", width=width, vocab=32000, max_positions=8192, norm=dict(eps=1e-6),
                 embedding=dict(scale=float(width) ** 0.5), residual_mult=0.5, loop=dict(start=0, stop=1, times=2),
                 layers=layers)
+
+
+def mobunex_config(width: int) -> dict:
+    """Four layers at the sizes of a real model of this kind: latent attention (heads of 128 + 64
+    rotated, a latent of 512, YaRN-stretched rotation), windowed attention with an eighth as many
+    key/value heads, a gated linear recurrence as wide as the model in blocks of 256 with 4 taps; a
+    window of 1,024 everywhere; 32 experts of a quarter of the dense width, 4 chosen from the best 2 of
+    4 groups, and a shared expert of the same width."""
+    heads, ff = width // 128, {2048: 5632, 4096: 11008}.get(width, width * 11 // 4)
+    lat = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=width * 3 // 4, scale=192 ** -0.5,
+               mask=dict(size=1024), rot=dict(base=1000000.0, dims=64,
+                                              scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)))
+    win = dict(heads=heads, kv_heads=max(1, heads // 8), dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=1024))
+    rec = dict(width=width, blocks=max(1, width // 256), conv=4)
+    dense = dict(kind="dense", ff=ff)
+    moe = dict(kind="moe", expert=dict(ff=ff // 4), router=dict(experts=32, top=4, groups=dict(count=4, keep=2)),
+               shared=dict(ff=ff // 4))
+    layers = [dict(type="latent_attention", mixer=lat, mlp=dense), dict(type="attention", mixer=win, mlp=moe),
+              dict(type="rglru", mixer=rec, mlp=moe), dict(type="latent_attention", mixer=lat, mlp=moe)][:LAYERS]
+    return dict(architecture="Mobunex", width=width, vocab=32000, norm=dict(eps=1e-6), postln_alpha=2.0, layers=layers)
 
 
 def qwen_config(width: int, design: str = "gebadra") -> dict:
@@ -283,6 +304,62 @@ def rooflines_gusorax(width: int, pk: dict):
             "decode": both(R, R * min(C + 1, W), R * min(C + 1, W), R * (C + 1), R * (C + 1))}
 
 
+def rooflines_mobunex(width: int, pk: dict):
+    """Algorithmic bytes and FLOPs of the compared kernels for the two workloads, per launch; Bavetar's
+    kernels (the model beside it) come from ``rooflines_bavetar``.  ``unit_norm`` is the mean over a
+    step's launches: a norm between the sublayers moves 12 bytes an element, a layer's last norm also
+    reads every earlier layer's result for the mix over depth and writes the mix."""
+    m = mobunex_config(width)
+    lat, win, rec = m["layers"][0]["mixer"], m["layers"][1]["mixer"], m["layers"][2]["mixer"]
+    H, D, Rr, rank = lat["heads"], lat["dim"], lat["rot_dim"], lat["kv_rank"]
+    dk = rank + Rr
+    WH, WG, WD, WE, Wn = win["heads"], win["kv_heads"], win["dim"], win["vdim"], win["mask"]["size"]
+    C, n = rec["width"], rec["width"] // rec["blocks"]
+    ff = m["layers"][0]["mlp"]["ff"]
+    r = m["layers"][1]["mlp"]
+    E, top, eff = r["router"]["experts"], r["router"]["top"], r["expert"]["ff"]
+    T, R, Cx = PROMPT, BATCH, PROMPT
+    base = rooflines_bavetar(width, pk)
+
+    def t_us(by, fl):
+        return max(by / (pk["hbm_gbs"] * 1e9), fl / (pk["bf16_tflops"] * 1e12)) * 1e6
+
+    def both(rows, keys_total, keys_read, requests):
+        norm_bytes, launches = 0, 0
+        for i, layer in enumerate(m["layers"]):
+            if layer["mlp"] is not None:
+                norm_bytes += rows * width * (4 + 2 + 4 + 2)
+                launches += 1
+            norm_bytes += rows * width * (4 + 2 + 4 + 4 * (i + 1) + 4 + 2)
+            launches += 1
+        norm_bytes += R * width * (4 + 2) if rows == R else width * (4 + 2)      # the final norm's few rows
+        launches += 1
+        proj = (WH * WD + WG * (WD + WE)) * 2
+        return {
+            "unit_norm": t_us(norm_bytes / launches, 0),
+            "embedding_unit_norm": t_us(rows * width * (2 + 4 + 2), 0),
+            # the gates: two block-diagonal products in 32-bit arithmetic, and the coefficients out
+            "recurrence_gates": t_us(2 * rows * C + 2 * 2 * C * n + 8 * rows * C, 4 * rows * C * n),
+            "gated_scan": t_us(rows * C * (4 + 4 + 2 + 2) + 8 * requests * C, 0),
+            "short_conv": t_us(2 * rows * C * 2, 0),
+            "masked_attention": t_us(2 * rows * WH * WD + 2 * keys_read * WG * (WD + WE) + 2 * rows * WH * WE,
+                                     2 * WH * (WD + WE) * keys_total),
+            "head_norm_write": t_us(rows * proj + 2 * rows * WH * WD + 2 * rows * WG * (WD + WE), 0),
+            "latent_attention": t_us(4 * rows * H * dk + 2 * keys_read * dk + 4 * rows * H * rank,
+                                     2 * H * (dk + rank) * keys_total),
+            "latent_prepare": base["prefill" if rows == T else "decode"]["latent_prepare"],
+            "silu_mul": t_us(rows * ff * 6, 0),
+            "expert_rows": t_us(2 * min(E, rows * top) * 3 * eff * width, 6 * rows * top * eff * width),
+            "route": t_us(rows * E * 4, 0),
+        }
+    keys_prefill = sum(min(t + 1, Wn) for t in range(T))
+    out = {"prefill": both(T, keys_prefill, T, 1), "decode": both(R, R * min(Cx + 1, Wn), R * min(Cx + 1, Wn), R)}
+    for phase in out:
+        for k, v in base[phase].items():
+            out[phase].setdefault(k, v)
+    return out
+
+
 def rooflines(width: int, pk: dict):
     """Algorithmic bytes and FLOPs of the compared kernels for the two workloads, per launch."""
     g = gebadra_config(width)
@@ -320,8 +397,8 @@ def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
     from bench import ClockSampler, peaks
     from paged_batch_engine_b200.config import load_config
     from paged_batch_engine_b200.engine.runner import ModelRunner
-    if design not in ("gebadra", "bavetar", "gusorax"):
-        raise SystemExit(f"unknown design {design!r}; known: gebadra, bavetar, gusorax")
+    if design not in ("gebadra", "bavetar", "gusorax", "mobunex"):
+        raise SystemExit(f"unknown design {design!r}; known: gebadra, bavetar, gusorax, mobunex")
     os.environ["PBE_EXEC"] = "python"        # per-kernel times need every launch to come through ops
     pk = peaks()
     page = 16
@@ -339,15 +416,27 @@ def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
                "gated_activation", "silu_mul", "route", "expert_rows", "expert_places", "expert_gather", "expert_scatter",
                "grouped_runs", "run_tiles"]
         theirs = theirs + ["silu_mul"]
-    design_config = {"bavetar": bavetar_config, "gusorax": gusorax_config}.get(design, gebadra_config)
-    roofs = {"bavetar": rooflines_bavetar, "gusorax": rooflines_gusorax}.get(design, rooflines)
+    bavetar_ops = ["latent_attention", "head_product", "latent_prepare", "add2_rmsnorm2", "linear_attention",
+                   "short_conv", "step_sizes", "gated_rms", "relu_squared", "route", "expert_rows", "expert_places",
+                   "expert_gather", "expert_scatter", "grouped_heads", "grouped_runs", "run_tiles"]
+    beside, beside_config = "qwen2", lambda width: qwen_config(width, design)
+    if design == "mobunex":
+        own = ["unit_norm", "embedding_unit_norm", "recurrence_gates", "gated_scan", "short_conv", "masked_attention",
+               "head_norm_write", "latent_attention", "latent_prepare", "grouped_heads", "silu_mul", "route",
+               "expert_rows", "expert_places", "expert_gather", "expert_scatter", "grouped_runs", "run_tiles"]
+        theirs = bavetar_ops
+        beside, beside_config = "bavetar", bavetar_config
+    design_config = {"bavetar": bavetar_config, "gusorax": gusorax_config, "mobunex": mobunex_config}.get(
+        design, gebadra_config)
+    roofs = {"bavetar": rooflines_bavetar, "gusorax": rooflines_gusorax, "mobunex": rooflines_mobunex}.get(
+        design, rooflines)
     sampler = ClockSampler(0)
     sampler.active = True
     out = {}
     for width in sizes:
         roof = roofs(width, pk)
         row = {}
-        for name, cfg, names in ((design, design_config(width), own), ("qwen2", qwen_config(width, design), theirs)):
+        for name, cfg, names in ((design, design_config(width), own), (beside, beside_config(width), theirs)):
             _, typed = load_config(cfg)
             runner = ModelRunner.from_random(typed, seed=0, dtype="bfloat16", page_tokens=page, max_cache_tokens=pool,
                                              max_requests=BATCH + 1)
@@ -370,7 +459,9 @@ def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
             torch.cuda.empty_cache()
         out[str(width)] = row
     sampler.active = False
-    return {"design": design, "beside": "qwen2 at equal width, heads, key/value heads, feed-forward, vocabulary, layers",
+    return {"design": design,
+            "beside": f"{beside} at equal width, heads, feed-forward, vocabulary and layers"
+            + (", key/value heads" if beside == "qwen2" else ""),
             "layers": LAYERS, "prompt_tokens": PROMPT, "decode_batch": BATCH, "decode_context": PROMPT,
             "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic (random weights)",
             "peaks": {"source": pk["source"], "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},

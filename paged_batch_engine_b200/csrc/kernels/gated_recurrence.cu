@@ -11,6 +11,9 @@
 //   two maps a thread; the epilogue turns them into the recurrence's coefficients a and
 //   b = sqrt(1 - a^2) i u, float32 [T, C] each.  1 - a^2 is taken as -expm1(2 log a): exact where a
 //   is close to one.
+//   Where the input and the maps are bfloat16 the products may instead run on the tensor cores (every
+//   product of two bfloat16 numbers is exact in float32 and the sums are float32): the scan then
+//   takes the gates' pre-activations z = [R_b u_b | I_b u_b] and forms a and b itself, row by row.
 // gated_scan: a thread a channel walks an item's rows in order.  An item is (first row, rows, state
 //   from, state to); a place is a state row (>= 0), nothing (-1: start from zero / keep nothing) or
 //   scratch entry -(v + 2).  A step's requests are the items themselves (items == null), or, for long
@@ -106,8 +109,16 @@ __global__ void __launch_bounds__(256) recurrence_gates_kernel(GateParams p) {
 
 // ------------------------------------------------------------------------------------------------
 struct ScanParams {
-  const float* a;            // [T, C]
+  const float* a;            // [T, C], or null: the coefficients are formed from z
   const float* b;            // [T, C]
+  const float* z;            // [T, B, 2n]: per block the recurrence gate's n pre-activations, then the input gate's
+  const void* u;             // [T, ldu]: the recurrence's input (with z)
+  int ldu;
+  const float* b_r;          // [C] gate biases and lam (with z)
+  const float* b_i;
+  const float* lam;
+  float rate;
+  int n;                     // channels a block (with z)
   const void* y;             // [T, ldy]: the gate branch before its activation, or null
   int ldy;
   void* out;                 // [T, C] or null (first pass)
@@ -145,13 +156,33 @@ __global__ void gated_scan_kernel(ScanParams p) {
   if (from >= 0) S = p.state[(size_t)from * p.C + c];
   else if (from < -1) S = p.scratch_s[(size_t)(-(from + 2)) * p.C + c];
   float prod = 1.f;
-  const float* a = p.a + (size_t)first * p.C + c;
-  const float* b = p.b + (size_t)first * p.C + c;
+  const bool from_z = p.a == nullptr;
+  const float* a = from_z ? nullptr : p.a + (size_t)first * p.C + c;
+  const float* b = from_z ? nullptr : p.b + (size_t)first * p.C + c;
+  const int blk = from_z ? c / p.n : 0;
+  // block blk's 2n pre-activations start at column blk * 2n: the recurrence gate's, then the input gate's
+  const float* zr = from_z ? p.z + (size_t)first * 2 * p.C + (size_t)blk * 2 * p.n + (c - blk * p.n) : nullptr;
+  const T* u = from_z ? (const T*)p.u + (size_t)first * p.ldu + c : nullptr;
+  float neg_rate_sp = 0.f, br = 0.f, bi = 0.f;
+  if (from_z) {
+    neg_rate_sp = -p.rate * softplus_f(p.lam[c]);
+    br = p.b_r[c];
+    bi = p.b_i[c];
+  }
   const T* y = p.y ? (const T*)p.y + (size_t)first * p.ldy + c : nullptr;
   T* out = p.out ? (T*)p.out + (size_t)first * p.C + c : nullptr;
   for (int t = 0; t < rows; ++t) {
-    const float at = a[(size_t)t * p.C];
-    S = fmaf(at, S, b[(size_t)t * p.C]);
+    float at, bt;
+    if (from_z) {
+      const float* zt = zr + (size_t)t * 2 * p.C;
+      const float log_a = neg_rate_sp * sigmoid_f(zt[0] + br);
+      at = expf(log_a);
+      bt = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(zt[p.n] + bi) * to_float(u[(size_t)t * p.ldu]);
+    } else {
+      at = a[(size_t)t * p.C];
+      bt = b[(size_t)t * p.C];
+    }
+    S = fmaf(at, S, bt);
     prod *= at;
     if (out) {
       float v = S;
@@ -208,14 +239,18 @@ PBE_EXPORT int pbe_recurrence_gates(const void* u, int ldu, int u_dtype, const v
 }
 
 // mode 0: every request one item (from the step's own arrays); 1: first pass over `items`; 2: second pass.
-PBE_EXPORT int pbe_gated_scan(const float* a, const float* b, const void* y, int ldy, void* out, int dtype, float* state,
+PBE_EXPORT int pbe_gated_scan(const float* a, const float* b, const float* z, const void* u, int ldu, const float* b_r,
+                              const float* b_i, const float* lam, float rate, int n, const void* y, int ldy, void* out,
+                              int dtype, float* state,
                               float* scratch_s, float* scratch_p, const int32_t* items, int num_items,
                               const int32_t* q_start, const int32_t* q_len, const int32_t* slots, int C, int act,
                               int mode, cudaStream_t stream) {
   if (num_items <= 0 || C <= 0) return 0;
   if ((mode != 0 && items == nullptr) || (mode == 0 && (q_start == nullptr || q_len == nullptr || slots == nullptr)))
     return (int)cudaErrorInvalidValue;
-  ScanParams p{a, b, mode == 1 ? nullptr : y, ldy, mode == 1 ? nullptr : out, state, scratch_s, scratch_p,
+  if ((a == nullptr) != (z != nullptr) || (z != nullptr && (n < 1 || C % n != 0 || !u || !b_r || !b_i || !lam)))
+    return (int)cudaErrorInvalidValue;
+  ScanParams p{a, b, z, u, ldu, b_r, b_i, lam, rate, n, mode == 1 ? nullptr : y, ldy, mode == 1 ? nullptr : out, state, scratch_s, scratch_p,
                mode == 0 ? nullptr : items, q_start, q_len, slots, C, act, mode == 1 ? 1 : 0};
   const int threads = C >= 128 ? 128 : 64;
   dim3 grid(num_items, (C + threads - 1) / threads);

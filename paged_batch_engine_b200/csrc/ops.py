@@ -1844,17 +1844,55 @@ def recurrence_gates(u: torch.Tensor, w_r: torch.Tensor, w_i: torch.Tensor, b_r:
 SCAN_ACTIVATIONS = {None: 0, "gelu_tanh": 1}
 
 
-def gated_scan(a: torch.Tensor, b: torch.Tensor, y: Optional[torch.Tensor], state: torch.Tensor, q_start: torch.Tensor,
-               q_len: torch.Tensor, slots: torch.Tensor, num_requests: int, out_dtype: torch.dtype,
-               activation: Optional[str] = "gelu_tanh", plan=None, zero_out: bool = False) -> torch.Tensor:
+def gate_products(u: torch.Tensor, w_gates: torch.Tensor) -> torch.Tensor:
+    """z, float32 [T, B, 2n]: per block b of the channels the pre-activations [R_b u_b | I_b u_b] of both
+    gates, on the tensor cores; ``u`` bfloat16 [T, B*n] (possibly a column slice), ``w_gates`` bfloat16
+    [B, 2n, n], a block's recurrence-gate rows followed by its input-gate rows.  Products of two
+    bfloat16 numbers are exact in float32 and the sums are float32."""
+    _need_cuda(u, w_gates)
+    _need_contiguous(w_gates)
+    _column_slice(u, "gate_products")
+    T, C = u.shape
+    B, n2, n = w_gates.shape
+    if n2 != 2 * n or B * n != C or u.dtype != torch.bfloat16 or w_gates.dtype != torch.bfloat16:
+        raise KernelError("gate_products: bfloat16 input [T, B*n] and maps [B, 2n, n]")
+    z = torch.empty((T, B, 2 * n), dtype=torch.float32, device=u.device)
+    ld = u.stride(0) if T > 1 else max(u.stride(0), C)
+    return grouped_heads(u, ld, n, n, w_gates, 2 * n * n, 1, n, 2 * n, z, B * 2 * n, 2 * n, T, B)
+
+
+def gated_scan(a: Optional[torch.Tensor], b: Optional[torch.Tensor], y: Optional[torch.Tensor], state: torch.Tensor,
+               q_start: torch.Tensor, q_len: torch.Tensor, slots: torch.Tensor, num_requests: int,
+               out_dtype: torch.dtype, activation: Optional[str] = "gelu_tanh", plan=None, zero_out: bool = False,
+               gates: Optional[tuple] = None) -> torch.Tensor:
     """S_t = a_t S_(t-1) + b_t per channel over each request's rows, from and to the request's row of
     ``state`` (float32 [slots, C]); returns S_t * act(y_t) as [T, C] in ``out_dtype`` (``y`` [T, C],
     possibly a column slice, or None: S itself).  ``plan`` (a ``RecurrencePlan`` with chunks): long
-    portions run as chunks side by side, in three launches."""
+    portions run as chunks side by side, in three launches.  Instead of ``a`` and ``b``, ``gates`` =
+    (z, u, b_r, b_i, lam, rate) with z from ``gate_products``: the scan forms the coefficients of
+    ``recurrence_gates`` itself, row by row, in float32."""
     _need_cuda(a, b, y, state, q_start, q_len, slots)
     _need_contiguous(a, b, state)
-    T, C = a.shape
-    if a.dtype != torch.float32 or b.dtype != torch.float32 or b.shape != a.shape:
+    z = u = b_r = b_i = lam = None
+    rate, n, ldu = 0.0, 0, 0
+    if gates is not None:
+        if a is not None or b is not None:
+            raise KernelError("gated_scan: coefficients or gates, not both")
+        z, u, b_r, b_i, lam, rate = gates
+        _need_cuda(z, u, b_r, b_i, lam)
+        _need_contiguous(z, b_r, b_i, lam)
+        _column_slice(u, "gated_scan")
+        T, C = u.shape
+        n = z.shape[2] // 2
+        if z.dtype != torch.float32 or z.dim() != 3 or z.shape[0] != T or z.shape[1] * n != C or u.dtype != out_dtype:
+            raise KernelError("gated_scan: z is float32 [T, B, 2n], u [T, B*n] in the output's dtype")
+        for v in (b_r, b_i, lam):
+            if v.dtype != torch.float32 or v.numel() != C:
+                raise KernelError("gated_scan: gate biases and lam are float32 [C]")
+        ldu = u.stride(0) if T > 1 else max(u.stride(0), C)
+    else:
+        T, C = a.shape
+    if gates is None and (a.dtype != torch.float32 or b.dtype != torch.float32 or b.shape != a.shape):
         raise KernelError("gated_scan: a and b are float32 [T, C]")
     if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != C:
         raise KernelError("gated_scan: the state is float32 [slots, C]")
@@ -1863,26 +1901,29 @@ def gated_scan(a: torch.Tensor, b: torch.Tensor, y: Optional[torch.Tensor], stat
     ldy = 0
     if y is not None:
         _column_slice(y, "gated_scan")
-        if y.shape != a.shape or y.dtype != out_dtype:
+        if tuple(y.shape) != (T, C) or y.dtype != out_dtype:
             raise KernelError("gated_scan: y is [T, C] in the output's dtype")
         ldy = y.stride(0) if T > 1 else max(y.stride(0), C)
-    out = (torch.zeros if zero_out else torch.empty)((T, C), dtype=out_dtype, device=a.device)
+    dev = state.device
+    out = (torch.zeros if zero_out else torch.empty)((T, C), dtype=out_dtype, device=dev)
     fn = _fn("gated_recurrence", "pbe_gated_scan",
-             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
+              c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     code, act = _dtype_code(out), SCAN_ACTIVATIONS[activation]
+    coeff = (_ptr(a), _ptr(b), _ptr(z), _ptr(u), int(ldu), _ptr(b_r), _ptr(b_i), _ptr(lam), float(rate), int(n))
     if plan is None or plan.num_chunks == 0:
-        _check(fn(_ptr(a), _ptr(b), _ptr(y), ldy, _ptr(out), code, _ptr(state), None, None, None, int(num_requests),
+        _check(fn(*coeff, _ptr(y), ldy, _ptr(out), code, _ptr(state), None, None, None, int(num_requests),
                   _ptr(q_start), _ptr(q_len), _ptr(slots), C, act, 0, _stream()), "gated_scan")
         return out
-    scratch_s = torch.empty((plan.num_chunks, C), dtype=torch.float32, device=a.device)
-    scratch_p = torch.empty((plan.num_chunks, C), dtype=torch.float32, device=a.device)
+    scratch_s = torch.empty((plan.num_chunks, C), dtype=torch.float32, device=dev)
+    scratch_p = torch.empty((plan.num_chunks, C), dtype=torch.float32, device=dev)
     if plan.num_first_pass:
-        _check(fn(_ptr(a), _ptr(b), None, 0, None, code, _ptr(state), _ptr(scratch_s), _ptr(scratch_p),
+        _check(fn(*coeff, None, 0, None, code, _ptr(state), _ptr(scratch_s), _ptr(scratch_p),
                   _ptr(plan.first_pass), plan.num_first_pass, None, None, None, C, act, 1, _stream()), "gated_scan")
     sfn = _fn("gated_recurrence", "pbe_chunk_starts", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
     _check(sfn(_ptr(plan.scan), plan.num_scan, _ptr(state), _ptr(scratch_s), _ptr(scratch_p), C, _stream()),
            "chunk_starts")
-    _check(fn(_ptr(a), _ptr(b), _ptr(y), ldy, _ptr(out), code, _ptr(state), _ptr(scratch_s), _ptr(scratch_p),
+    _check(fn(*coeff, _ptr(y), ldy, _ptr(out), code, _ptr(state), _ptr(scratch_s), _ptr(scratch_p),
               _ptr(plan.second_pass), plan.num_second_pass, None, None, None, C, act, 2, _stream()), "gated_scan")
     return out

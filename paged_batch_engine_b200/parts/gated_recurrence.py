@@ -1,6 +1,7 @@
 """A gated diagonal linear recurrence behind a short causal convolution, times an activated branch."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -21,6 +22,11 @@ class GatedLinearRecurrence(Mixer):
     from S = 0 (no special case for the first token); the output is W_o (S * y).  S is float32, kept
     per request, as are the convolution's last taps - 1 inputs; gates, decays and the recurrence are
     float32.  ``activation``: "gelu_tanh".
+
+    In bfloat16 runs the gates' products run on the tensor cores (``ops.gate_products``: products of
+    two bfloat16 numbers are exact in float32, the sums are float32) and the scan forms a and b from
+    the pre-activations on its way; float32 runs take ``ops.recurrence_gates`` (float32 FMAs).
+    ``PBE_GATES=fma`` keeps bfloat16 runs on the latter too.
 
     Checkpoint tensors under the prefix (names in ``tensor_names``): y, x [width, hidden] with biases
     ``.b``, conv [width, taps], conv.b, ra, ri [blocks, width/blocks, width/blocks] ([out, in]) with
@@ -45,7 +51,7 @@ class GatedLinearRecurrence(Mixer):
         self.rate, self.activation = float(rate), activation
         self.dtype, self.device = dtype, device
         self.w_in = self.b_in = self.w_o = self.conv_w = self.conv_wt = self.conv_b = None
-        self.w_r = self.w_i = self.b_r = self.b_i = self.lam = None
+        self.w_r = self.w_i = self.b_r = self.b_i = self.lam = self.w_gates = None
 
     def cache_need(self):
         need = dict(rec=StateNeed((self.width,), torch.float32))
@@ -54,7 +60,8 @@ class GatedLinearRecurrence(Mixer):
         return CompositeNeed.of(**need)
 
     def kernel_libraries(self, dtype):
-        return [("short_conv", None), ("gated_recurrence", None)] + ops.gemm_libraries(dtype)
+        tiled = [("grouped_gemm", None)] if dtype == torch.bfloat16 else []
+        return [("short_conv", None), ("gated_recurrence", None)] + tiled + ops.gemm_libraries(dtype)
 
     def param_specs(self, prefix):
         n, w, C, B = self.names, self.hidden_size, self.width, self.blocks
@@ -87,6 +94,9 @@ class GatedLinearRecurrence(Mixer):
         self.b_r = f32(n["gate_a"] + b).reshape(-1).contiguous()
         self.b_i = f32(n["gate_i"] + b).reshape(-1).contiguous()
         self.lam = f32(n["lam"])
+        if self.w_r.dtype == torch.bfloat16 and os.environ.get("PBE_GATES", "").strip().lower() != "fma":
+            # a block's recurrence-gate rows followed by its input-gate rows: one product gives both
+            self.w_gates = torch.cat([self.w_r, self.w_i], dim=1).contiguous()
 
     def chunk_rows(self, rows: int) -> int:
         """Rows of a chunk when a long portion's recurrence runs as chunks side by side: so long that
@@ -108,14 +118,19 @@ class GatedLinearRecurrence(Mixer):
         u = ops.short_conv(x_in, self.conv_w, self.conv_b, conv_state, ctx.request_of_row, ctx.q_start, ctx.q_len,
                            ctx.state_slots, ctx.num_requests, silu=False, update_state=cache.writes,
                            weight_t=self.conv_wt)
-        a, b = ops.recurrence_gates(u, self.w_r, self.w_i, self.b_r, self.b_i, self.lam, self.rate)
+        if self.w_gates is not None and u.dtype == torch.bfloat16:
+            a = b = None
+            gates = (ops.gate_products(u, self.w_gates), u, self.b_r, self.b_i, self.lam, self.rate)
+        else:
+            a, b = ops.recurrence_gates(u, self.w_r, self.w_i, self.b_r, self.b_i, self.lam, self.rate)
+            gates = None
         captured = getattr(ctx, "captured", False)
         plan = None if captured else ctx.recurrence_plan(self.chunk_rows(ctx.num_tokens))
         state = cache.sub["rec"].state
         if not cache.writes:
             state = state.clone()
         out = ops.gated_scan(a, b, y, state, ctx.q_start, ctx.q_len, ctx.state_slots, ctx.num_requests, self.dtype,
-                             self.activation, plan, zero_out=captured)
+                             self.activation, plan, zero_out=captured, gates=gates)
         return ops.linear(out, self.w_o, None, out_dtype=self.dtype, kind=2)
 
 

@@ -137,6 +137,40 @@ def test_recurrence_gates_and_coefficients(C, B, dt):
     assert torch.allclose(b.cpu().double(), b_want, atol=2e-6, rtol=3e-5)
 
 
+@pytest.mark.parametrize("C, B", [(48, 3), (160, 1), (70, 7), (256, 2), (40, 5)])
+def test_gates_on_the_tensor_cores_and_coefficients_formed_in_the_scan(C, B):
+    """bfloat16 input and maps: the products on the tensor cores are sums of exact products, so the
+    scan that forms a and b from them equals the recurrence on float64 gates of the same numbers."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(C * 3 + B)
+    lens, starts, slots = [50, 1, 13], [0, 50, 51], [2, 0, 1]
+    T = sum(lens)
+    wide = torch.randn(T, 2 * C + 5, generator=g).to(torch.bfloat16)
+    u, y = wide[:, 3:3 + C], wide[:, 3 + C:3 + 2 * C]
+    w = _gate_weights(C, B, g, torch.bfloat16)
+    r, i = _plain_coefficients(u.double(), w)
+    want = torch.cat([pm.gated_recurrence(u[s:s + n].double(), r[s:s + n], i[s:s + n], w["lam"].double())
+                      for s, n in zip(starts, lens)]) * pm.gelu_tanh(y.double())
+    dev = wide.to(DEV)
+    du, dy = dev[:, 3:3 + C], dev[:, 3 + C:3 + 2 * C]
+    z = ops.gate_products(du, torch.cat([w["ra"], w["ri"]], dim=1).contiguous().to(DEV))
+    n = C // B
+    zr = torch.einsum("tbi,boi->tbo", u.double().reshape(T, B, n), w["ra"].double())
+    assert torch.allclose(z[:, :, :n].cpu().double(), zr, atol=1e-5, rtol=1e-5)
+    state = torch.zeros(4, C, device=DEV)
+    gates = (z, du, w["rab"].reshape(-1).to(DEV), w["rib"].reshape(-1).to(DEV), w["lam"].to(DEV), 8.0)
+    got = ops.gated_scan(None, None, dy, state, i32(starts), i32(lens), i32(slots), 3, torch.bfloat16, gates=gates)
+    assert torch.allclose(got.float().cpu().double(), want, atol=2e-2, rtol=2e-2)
+    # S itself, in float32, is the sharper comparison
+    state.zero_()
+    S = ops.gated_scan(None, None, None, state, i32(starts), i32(lens), i32(slots), 3, torch.bfloat16, activation=None,
+                       gates=gates)
+    del S
+    ends = torch.stack([pm.gated_recurrence(u[s:s + n_].double(), r[s:s + n_], i[s:s + n_], w["lam"].double())[-1]
+                        for s, n_ in zip(starts, lens)])
+    assert torch.allclose(state[slots].cpu().double(), ends, atol=2e-5, rtol=2e-5)
+
+
 @pytest.mark.parametrize("C, dt", [(48, torch.float32), (130, torch.bfloat16)])
 def test_gated_scan_carries_its_state(C, dt):
     """Unequal requests in one launch equal each alone; a request cut into launches equals it whole;
