@@ -171,7 +171,8 @@ __global__ void gated_scan_kernel(ScanParams p) {
   }
   const T* y = p.y ? (const T*)p.y + (size_t)first * p.ldy + c : nullptr;
   T* out = p.out ? (T*)p.out + (size_t)first * p.C + c : nullptr;
-  for (int t = 0; t < rows; ++t) {
+#pragma unroll 4
+  for (int t = 0; t < rows; ++t) {     // unrolled: the rows' loads do not wait for one another, only S does
     float at, bt;
     if (from_z) {
       const float* zt = zr + (size_t)t * 2 * p.C;

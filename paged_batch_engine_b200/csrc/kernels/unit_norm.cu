@@ -16,6 +16,29 @@ using namespace pbe;
 
 namespace {
 
+// four consecutive elements, 16-byte aligned for float and 8-byte aligned for bfloat16
+__device__ __forceinline__ void load4(const float* p, float (&a)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&a)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  a[0] = __low2float(lo); a[1] = __high2float(lo); a[2] = __low2float(hi); a[3] = __high2float(hi);
+}
+__device__ __forceinline__ void store4(float* p, const float (&a)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(a[0], a[1], a[2], a[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&a)[4]) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a[0], a[1]);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(a[2], a[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&lo);
+  raw.y = *reinterpret_cast<unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 struct UnitNormParams {
   const float* x;            // [T, d]
   const void* y1;            // [T, d] or null
@@ -49,6 +72,57 @@ __global__ void unit_norm_kernel(UnitNormParams p) {
   const TD* y1 = p.y1 ? (const TD*)p.y1 + (size_t)src * d : nullptr;
   const TD* y2 = p.y2 ? (const TD*)p.y2 + (size_t)src * d : nullptr;
   float ss = 0.f;
+  float* sum_out = p.sum_out ? p.sum_out + (size_t)src * d : nullptr;
+  float* normed = p.normed ? p.normed + (size_t)r * d : nullptr;
+  float* mixed = p.mixed ? p.mixed + (size_t)r * d : nullptr;
+  TO* lp = p.lp ? (TO*)p.lp + (size_t)r * d : nullptr;
+  const float* hist = p.history ? p.history + (size_t)src * d : nullptr;
+  if ((d & 3) == 0 && (p.history_stride & 3) == 0) {
+    // four elements a thread: 16-byte accesses of the float32 tensors, 8-byte ones of the bfloat16
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float v[4], a[4];
+      load4(x + i, v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] *= p.alpha;
+      if (y1) {
+        load4(y1 + i, a);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] += a[k];
+      }
+      if (y2) {
+        load4(y2 + i, a);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] += a[k];
+      }
+      store4(row + i, v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ss = fmaf(v[k], v[k], ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + p.eps);
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float v[4], n[4];
+      load4(row + i, v);
+      if (sum_out) store4(sum_out + i, v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) n[k] = (v[k] * inv) * g;
+      if (normed) store4(normed + i, n);
+      if (p.mix) {
+        float m[4] = {0.f, 0.f, 0.f, 0.f}, h[4];
+        for (int j = 0; j < p.n_prev; ++j) {
+          const float w = p.mix[j];
+          load4(hist + (size_t)j * p.history_stride + i, h);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) m[k] = fmaf(w, h[k], m[k]);
+        }
+        const float w = p.mix[p.n_prev];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) n[k] = fmaf(w, n[k], m[k]);
+        if (mixed) store4(mixed + i, n);
+      }
+      if (lp) store4(lp + i, n);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = p.alpha * x[i];
     if (y1) v += to_float(y1[i]);
@@ -57,11 +131,6 @@ __global__ void unit_norm_kernel(UnitNormParams p) {
     ss = fmaf(v, v, ss);
   }
   const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + p.eps);
-  float* sum_out = p.sum_out ? p.sum_out + (size_t)src * d : nullptr;
-  float* normed = p.normed ? p.normed + (size_t)r * d : nullptr;
-  float* mixed = p.mixed ? p.mixed + (size_t)r * d : nullptr;
-  TO* lp = p.lp ? (TO*)p.lp + (size_t)r * d : nullptr;
-  const float* hist = p.history ? p.history + (size_t)src * d : nullptr;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float v = row[i];
     if (sum_out) sum_out[i] = v;
@@ -120,7 +189,7 @@ PBE_EXPORT int pbe_unit_norm(const float* x, const void* y1, const void* y2, int
   if (d < 1 || smem > 200 * 1024 || n_prev < 0 || (mix && n_prev > 0 && !history)) return (int)cudaErrorInvalidValue;
   UnitNormParams p{x, y1, y2, alpha, gain, eps, sum_out, normed, history, history_stride, mix ? n_prev : 0, mix, mixed,
                    lp, row_index, d};
-  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
 #define PBE_UN(TD, TO)                                                        \
   do {                                                                        \
     opt_in(unit_norm_kernel<TD, TO>, smem);                                   \
