@@ -340,7 +340,8 @@ def rooflines_mobunex(width: int, pk: dict):
             "embedding_unit_norm": t_us(rows * width * (2 + 4 + 2), 0),
             # the gates: two block-diagonal products in 32-bit arithmetic, and the coefficients out
             "recurrence_gates": t_us(2 * rows * C + 2 * 2 * C * n + 8 * rows * C, 4 * rows * C * n),
-            "gated_scan": t_us(rows * C * (4 + 4 + 2 + 2) + 8 * requests * C, 0),
+            # the gates' float32 pre-activations (two a channel), the input and the branch in, the product out
+            "gated_scan": t_us(rows * C * (8 + 2 + 2 + 2) + 8 * requests * C, 0),
             "short_conv": t_us(2 * rows * C * 2, 0),
             "masked_attention": t_us(2 * rows * WH * WD + 2 * keys_read * WG * (WD + WE) + 2 * rows * WH * WE,
                                      2 * WH * (WD + WE) * keys_total),
