@@ -90,7 +90,7 @@ def mobunex_config(width: int) -> dict:
                shared=dict(ff=ff // 4))
     layers = [dict(type="latent_attention", mixer=lat, mlp=dense), dict(type="attention", mixer=win, mlp=moe),
               dict(type="rglru", mixer=rec, mlp=moe), dict(type="latent_attention", mixer=lat, mlp=moe)][:LAYERS]
-    return dict(architecture="Mobunex", width=width, vocab=32000, norm=dict(eps=1e-6), postln_alpha=2.0, layers=layers)
+    return dict(architecture="Mobunex", width=width, vocab=32000, norm=dict(eps=1e-6), postln_alpha=1.5, layers=layers)
 
 
 def qwen_config(width: int, design: str = "gebadra") -> dict:
