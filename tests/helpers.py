@@ -409,12 +409,12 @@ MOB_C = dict(
 MOBUNEX = {"A": (MOB_A, 51, 8), "B": (MOB_B, 52, 16), "C": (MOB_C, 53, 8)}     # config, seed, page tokens
 
 
-def make_mobunex_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str:
+def make_mobunex_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16, gain: float = 1.0) -> str:
     """A model folder with seeded random weights through the engine's random-weights mode, then
     reshaped so that no mechanism is a near-identity: projections large enough that every sublayer
     matters beside the skip path, sharp softmaxes, temperatures, gate biases and decay rates spread
     over a range, routers that decide and corrections that change the choice, depth mixes far from
-    "the last result only"."""
+    "the last result only".  ``gain`` scales the matrices' factors (wide models need less)."""
     from paged_batch_engine_b200.config import load_config
     from paged_batch_engine_b200.engine.runner import build_model
     from paged_batch_engine_b200.weights import write_random_model
@@ -431,11 +431,11 @@ def make_mobunex_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str
         if k.endswith(".b"):
             t = torch.randn(t.shape, generator=g) * 0.5
         elif leaf in ("q", "k", "dq", "dkv", "uq", "uk", "x", "y") and t.dim() == 2:
-            t = t * 6.0
+            t = t * 6.0 * gain
         elif leaf in ("v", "o", "g", "uv") and t.dim() == 2:
-            t = t * 6.0
+            t = t * 6.0 * gain
         elif leaf in ("ra", "ri"):
-            t = t * 12.0
+            t = t * 12.0 * gain
         elif leaf == "temp":
             t = 0.5 + 1.5 * torch.rand(t.shape, generator=g)
         elif leaf == "lam":
@@ -443,9 +443,9 @@ def make_mobunex_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str
         elif leaf == "conv":
             t = torch.randn(t.shape, generator=g) * 0.6
         elif leaf in ("up", "down", "gate") and t.dim() == 2:
-            t = t * 4.5
+            t = t * 4.5 * gain
         elif leaf == "router":
-            t = t * 12.0
+            t = t * 12.0 * gain
         elif leaf == "correction":
             t = torch.randn(t.shape, generator=g) * 0.3
         elif leaf == "dwa":

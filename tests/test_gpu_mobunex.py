@@ -582,6 +582,27 @@ def test_schedules_agree_with_plain(folders, name, dtype):
             assert runner.cache.num_free_pages(gi) == runner.cache.pools[gi].num_pages
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_real_widths(tmp_path, dtype):
+    """Heads of 128 (+ 64 rotated) over a latent of 512, windowed heads of 128 on one key head, a
+    recurrence of 512 channels in blocks of 256, sixteen experts: the widths at which the tensor-core
+    kernels run with their full tiles; a prompt, then tokens decoded past every window."""
+    from tests.helpers import _mlat, _mmoe, _mrec, _mwin
+    cfg = dict(architecture="Mobunex", width=512, vocab=640, norm=dict(eps=1e-6), postln_alpha=1.2, layers=[
+        dict(type="latent_attention", mixer=_mlat(4, 128, 64, 64, 128, 512, 384, 1000000.0, 192 ** -0.5, 100,
+                                                  (8.0, 128, 32.0, 1.0)), mlp=dict(kind="dense", ff=768)),
+        dict(type="attention", mixer=_mwin(4, 1, 128, 128, 90, 128 ** -0.5), mlp=_mmoe(128, 16, 4, 4, 2, shared=128)),
+        dict(type="rglru", mixer=_mrec(512, 2, 4), mlp=None),
+    ])
+    folder = make_mobunex_folder(tmp_path / "real", cfg, 61, gain=0.4)
+    g = torch.Generator().manual_seed(8)
+    reqs = {"r": torch.randint(0, cfg["vocab"], (190,), generator=g).tolist()}
+    want = plain_logits(folder, reqs)
+    recs = ru.tail_decoded(reqs, 30)
+    runner = make_runner(folder, dtype, 16, 256)
+    check(ru.run_records(runner, recs), want, dtype, "real widths")
+
+
 def test_batch_of_unequal_requests_equals_each_alone_and_slots_are_used_again(folders):
     """Eight requests through two request slots, two at a time, against each alone: a state row
     or a page that kept something of its former owner would show."""
