@@ -88,14 +88,15 @@ class MobunexConfig:
                 if m["conv"] > 16:
                     raise ConfigError(f"{mw}: at most 16 convolution taps are supported")
             elif kind == "attention":
-                for key in ("heads", "kv_heads", "dim", "vdim"):
+                for key in ("heads", "dim", "vdim"):
                     _positive(_need(m, key, mw), f"{mw}.{key}")
-                if m["heads"] % m["kv_heads"]:
+                if m["heads"] % _positive(m.get("kv_heads", m["heads"]), f"{mw}.kv_heads"):
                     raise ConfigError(f"{mw}: heads must be a multiple of kv_heads")
                 if m["dim"] > 256 or m["vdim"] > 256:
                     raise ConfigError(f"{mw}: heads are at most 256 wide")
                 _need(m, "scale", mw)
-                _positive(_need(_need(m, "mask", mw), "size", mw + ".mask"), "mask.size")
+                if m.get("mask") is not None:
+                    _positive(_need(m["mask"], "size", mw + ".mask"), "mask.size")
             else:
                 for key in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"):
                     _positive(_need(m, key, mw), f"{mw}.{key}")
@@ -104,7 +105,8 @@ class MobunexConfig:
                 if m["kv_rank"] > 512:
                     raise ConfigError(f"{mw}.kv_rank is at most 512")
                 _need(m, "scale", mw)
-                _positive(_need(_need(m, "mask", mw), "size", mw + ".mask"), "mask.size")
+                if m.get("mask") is not None:
+                    _positive(_need(m["mask"], "size", mw + ".mask"), "mask.size")
                 rot = _need(m, "rot", mw)
                 dims = _positive(_need(rot, "dims", mw + ".rot"), "rot.dims")
                 if dims % 2 or dims > m["rot_dim"]:
@@ -148,11 +150,13 @@ class MobunexConfig:
             return PartSpec("gated_linear_recurrence", dict(
                 hidden_size=self.width, width=int(m["width"]), blocks=int(m["blocks"]), conv_taps=int(m["conv"]),
                 rate=RGLRU_RATE, activation="gelu_tanh"))
+        window = int(m["mask"]["size"]) if m.get("mask") is not None else None     # no mask: every earlier token
         if layer["type"] == "attention":
             return PartSpec("masked_attention", dict(
-                hidden_size=self.width, num_heads=int(m["heads"]), num_kv_heads=int(m["kv_heads"]),
-                key_dim=int(m["dim"]), value_dim=int(m["vdim"]), scale=float(m["scale"]), eps=self.eps, mask="window",
-                mask_size=int(m["mask"]["size"]), qk_norm="unit", proj_bias="qkv", head_temperature=True))
+                hidden_size=self.width, num_heads=int(m["heads"]), num_kv_heads=int(m.get("kv_heads", m["heads"])),
+                key_dim=int(m["dim"]), value_dim=int(m["vdim"]), scale=float(m["scale"]), eps=self.eps,
+                mask="window" if window else None, mask_size=window, qk_norm="unit", proj_bias="qkv",
+                head_temperature=True))
         rot = m["rot"]
         rotary = dict(base=float(rot["base"]), dims=int(rot["dims"]))
         if rot.get("scaling"):
@@ -160,7 +164,7 @@ class MobunexConfig:
         return PartSpec("latent_attention", dict(
             hidden_size=self.width, num_heads=int(m["heads"]), head_dim=int(m["dim"]), rot_dim=int(m["rot_dim"]),
             value_dim=int(m["vdim"]), kv_rank=int(m["kv_rank"]), q_rank=int(m["q_rank"]), scale=float(m["scale"]),
-            eps=self.eps, rotary=rotary, sink=False, out_gate="each", window=int(m["mask"]["size"])))
+            eps=self.eps, rotary=rotary, sink=False, out_gate="each", window=window))
 
     def _mlp(self, mlp: Optional[dict]) -> Optional[PartSpec]:
         if mlp is None:

@@ -52,10 +52,14 @@ def softplus(x: Tensor) -> Tensor:
     return torch.where(x > 20, x, torch.log1p(torch.exp(torch.clamp(x, max=20))))
 
 
-def window_mask(positions: Tensor, size: int) -> Tensor:
-    """[T, T] bool: row i sees column j when 0 <= p_i - p_j < size."""
+def window_mask(positions: Tensor, size: Optional[int]) -> Tensor:
+    """[T, T] bool: row i sees column j when 0 <= p_i - p_j < size (no size: every earlier j)."""
     d = positions[:, None] - positions[None, :]
-    return (d >= 0) & (d < size)
+    return (d >= 0) & (d < size) if size else (d >= 0)
+
+
+def mask_size(m: dict) -> Optional[int]:
+    return int(m["mask"]["size"]) if m.get("mask") else None
 
 
 def masked_softmax(scores: Tensor, mask: Tensor) -> Tensor:
@@ -83,7 +87,7 @@ def post_norm(x: Tensor, y: Tensor, alpha: float, g: Tensor, eps: float) -> Tens
 # ---------------------------------------------------------------------------- attention
 def window_attention_mixer(h: Tensor, w: Dict[str, Tensor], p: str, m: dict, eps: float,
                            positions: Optional[Tensor] = None) -> Tensor:
-    H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, D, V = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
     T = h.shape[0]
     positions = torch.arange(T) if positions is None else positions
     q = (h @ w[p + "q"].t() + w[p + "q.b"]).reshape(T, H, D)
@@ -94,7 +98,7 @@ def window_attention_mixer(h: Tensor, w: Dict[str, Tensor], p: str, m: dict, eps
     k = k.repeat_interleave(per, dim=1)          # head h reads key/value head h // per
     v = v.repeat_interleave(per, dim=1)
     scores = torch.einsum("ihd,jhd->hij", q, k) * m["scale"] * w[p + "temp"][:, None, None]
-    wts = masked_softmax(scores, window_mask(positions, int(m["mask"]["size"])))
+    wts = masked_softmax(scores, window_mask(positions, mask_size(m)))
     out = torch.einsum("hij,jhv->ihv", wts, v).reshape(T, H * V)
     return out @ w[p + "o"].t()
 
@@ -194,7 +198,7 @@ def latent_attention_mixer(h: Tensor, w: Dict[str, Tensor], p: str, m: dict, eps
     k_plain = (c @ w[p + "uk"].t()).reshape(T, H, D)
     v = (c @ w[p + "uv"].t()).reshape(T, H, V)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihr,jr->hij", q_rot, k_rot)) * m["scale"]
-    wts = masked_softmax(scores, window_mask(positions, int(m["mask"]["size"])))
+    wts = masked_softmax(scores, window_mask(positions, mask_size(m)))
     out = torch.einsum("hij,jhv->ihv", wts, v).reshape(T, H * V)
     out = out * torch.sigmoid(h @ w[p + "g"].t())                            # a gate per output coordinate
     return out @ w[p + "o"].t()

@@ -603,6 +603,19 @@ def test_layers_of_real_widths(tmp_path, dtype):
     check(ru.run_records(runner, recs), want, dtype, "real widths")
 
 
+def test_layers_without_a_mask_see_every_earlier_token(tmp_path):
+    """A configuration whose attention layers name no mask (and no number of key heads)."""
+    import copy
+    cfg = copy.deepcopy(MOBUNEX["A"][0])
+    del cfg["layers"][0]["mixer"]["mask"], cfg["layers"][0]["mixer"]["kv_heads"], cfg["layers"][2]["mixer"]["mask"]
+    folder = make_mobunex_folder(tmp_path / "nomask", cfg, 71)
+    g = torch.Generator().manual_seed(9)
+    reqs = {"r": torch.randint(0, cfg["vocab"], (120,), generator=g).tolist()}
+    want = plain_logits(folder, reqs)
+    runner = make_runner(folder, "float32", 8, 128)
+    check(ru.run_records(runner, ru.tail_decoded(reqs, 30)), want, "float32", "no masks")
+
+
 def test_batch_of_unequal_requests_equals_each_alone_and_slots_are_used_again(folders):
     """Eight requests through two request slots, two at a time, against each alone: a state row
     or a page that kept something of its former owner would show."""

@@ -68,6 +68,15 @@ def test_what_the_mixers_keep():
     assert model.decode_capturable()
 
 
+def test_a_layer_without_a_mask_keeps_every_token():
+    cfg = copy.deepcopy(MOB_A)
+    del cfg["layers"][0]["mixer"]["mask"], cfg["layers"][0]["mixer"]["kv_heads"], cfg["layers"][2]["mixer"]["mask"]
+    model = build_model(load_config(cfg)[1], torch.float32, "cpu")
+    assert model.cache_needs[0].window is None and model.cache_needs[2].window is None
+    assert [(t.name, t.heads) for t in model.cache_needs[0].tensors] == [("k", 4), ("v", 4)]
+    assert torch.equal(pm.window_mask(torch.arange(4), None), torch.tril(torch.ones(4, 4, dtype=torch.bool)))
+
+
 @pytest.mark.parametrize("path, value, word", [
     (("layers", 0, "type"), "attention_9", "unknown layer type"),
     (("layers", 0, "mixer", "kv_heads"), 3, "multiple of kv_heads"),
